@@ -43,7 +43,8 @@ class RequestCache:
 class CacheManager:
     def __init__(self, needs, *, page_size: int, num_pages, max_requests: int, poison_freed: bool = False):
         """``needs``: per run ``("own", PagedKV|SlotState|None)``, or a tuple of those (at most one
-        of them paged; states with different names), or ``("borrow", run)`` (`CausalLM.cache_needs`).  ``num_pages``: pages per group (an int for all
+        of them paged; states with different names), or ``("borrow", run)``, or ``("borrow", run, states)`` for a run that
+        reads another run's pages and keeps `SlotState`s of its own (`CausalLM.cache_needs`).  ``num_pages``: pages per group (an int for all
         groups, or one per group).  ``poison_freed`` (a debugging aid, off by default): a page
         that goes back to its pool is filled with NaN in every layer and zeroed again when it is
         handed out, so that a read of a page the reader no longer holds shows in the logits."""
@@ -59,9 +60,13 @@ class CacheManager:
         self.run_group: dict[int, int] = {}        # run -> group (owning runs)
         self.state_runs: dict[int, list[SlotState]] = {}
         by_need: dict[PagedKV, int] = {}
-        for run, (how, what) in enumerate(self.needs):
+        for run, entry in enumerate(self.needs):
+            how, what = entry[0], entry[1]
             if how == "borrow":
-                continue
+                # the pages are the other run's; fixed-size state, if the layer keeps any, is this run's own
+                what = entry[2] if len(entry) > 2 else None
+                if any(not isinstance(n, SlotState) for n in flatten_needs(what)):
+                    raise TypeError(f"run {run}: a run that borrows a cache may only own state slots beside it")
             for need in flatten_needs(what):
                 if isinstance(need, PagedKV):
                     if run in self.run_group:
@@ -272,7 +277,8 @@ class CacheManager:
             (run, s.name): torch.zeros((self.max_requests + 1,) + tuple(s.shape), dtype=torch.float32, device=device)
             for run, states in self.state_runs.items() for s in states}
         caches: list[LayerCache] = []
-        for run, (how, what) in enumerate(self.needs):
+        for run, entry in enumerate(self.needs):
+            how, what = entry[0], entry[1]
             src = what if how == "borrow" else run
             cache = LayerCache()
             if src in self.run_group:
@@ -280,6 +286,8 @@ class CacheManager:
                 i = self.groups[gi].runs.index(src)
                 kv = self.kv_storage[gi][i]
                 cache.group, cache.k, cache.v = gi, kv[0], kv[1 if self.groups[gi].need.values else 0]
+            if how == "borrow" and run in self.state_runs:
+                src = run                     # (a borrowing run with state of its own keeps it apart from the lender's)
             if src in self.state_runs:
                 cache.states = {s.name: self.state_storage[(src, s.name)] for s in self.state_runs[src]}
                 cache.state = cache.states[self.state_runs[src][0].name]

@@ -41,6 +41,7 @@ struct AttnParams {
   int max_pages, page_size, nq, nkv, window, num_splits, total_tokens;
   int block;     // > 0: a query sees only keys of its own block of this many positions (counted from 0)
   float scale_log2;              // scale * log2(e)
+  const float* sink;             // [nq] or null: exp(sink_h) joins the softmax's denominator (no key, no value, not scaled)
 };
 
 constexpr int ATT_BN = 64;     // keys per tile
@@ -276,6 +277,7 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
       const int row = row0 + wrow + g + 8 * i;
       if (row >= rows_total) continue;
       const size_t orow = (size_t)(q0 + row / G) * p.nq + kvh * G + row % G;
+      if (p.sink != nullptr && p.num_splits == 1) l_r[i] += exp2f(p.sink[kvh * G + row % G] * 1.4426950408889634f - m_r[i]);
       const float inv = l_r[i] > 0.f ? 1.f / l_r[i] : 0.f;
       if (p.num_splits > 1) {
         float* po = p.part_o + ((size_t)split * p.total_tokens * p.nq + orow) * HD;
@@ -328,6 +330,7 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
         const float4 v = *reinterpret_cast<const float4*>(mo + (w * 16 + r) * HD + d4);
         acc.x += v.x * f[w]; acc.y += v.y * f[w]; acc.z += v.z * f[w]; acc.w += v.w * f[w];
       }
+      if (p.sink != nullptr && p.num_splits == 1) lt += exp2f(p.sink[kvh * G + row % G] * 1.4426950408889634f - mt);
       const float inv = lt > 0.f ? 1.f / lt : 0.f;
       const size_t orow = (size_t)(q0 + row / G) * p.nq + kvh * G + row % G;
       if (p.num_splits > 1) {
@@ -346,7 +349,8 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
 template <int HD>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                              __nv_bfloat16* __restrict__ out, int rows, int num_splits,
-                                             const int* __restrict__ tile_seq, const int* __restrict__ q_start, int nq) {
+                                             const int* __restrict__ tile_seq, const int* __restrict__ q_start, int nq,
+                                             const float* __restrict__ sink) {
   // One CTA per (tile, query head, token of the tile's request): the rows the decode form wrote and no others, so
   // that a step's other rows (a prompt portion's, the prefill form's) are neither read nor touched.  The step's
   // description is read before the wait for the kernel before.
@@ -363,6 +367,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
     const float l = part_lse[(size_t)s * rows + row];
     tot += l == -INFINITY ? 0.f : exp2f(l - mt);
   }
+  if (sink != nullptr) tot += exp2f(sink[blockIdx.y] * 1.4426950408889634f - mt);
   const float inv = tot > 0.f ? 1.f / tot : 0.f;
   for (int d = threadIdx.x; d < HD; d += blockDim.x) {
     float acc = 0.f;
@@ -396,7 +401,7 @@ static int launch_attention(const AttnParams& p, int tiles, cudaStream_t stream)
     const int G = p.nq / p.nkv;
     launch_kernel(attention_combine_kernel<HD>, dim3((unsigned)tiles, (unsigned)p.nq, (unsigned)(16 / G > 0 ? 16 / G : 1)), HD >= 128 ? 128 : 64, 0, stream,
                   (const float*)p.part_o, (const float*)p.part_lse, p.out, p.total_tokens * p.nq, p.num_splits, p.tile_seq,
-                  p.q_start, p.nq);
+                  p.q_start, p.nq, p.sink);
     rc = launch_status("attention_combine");
   }
   return rc;
@@ -416,7 +421,7 @@ SLLM_EXPORT int sllm_attention_mma(const void* q, const void* k_cache, const voi
                                    float* part_lse, const int* block_tables, int max_pages, const int* q_start,
                                    const int* ctx_len, const int* tile_seq, const int* tile_row0, int tiles,
                                    int decode, int num_splits, int total_tokens, int nq, int nkv, int hd,
-                                   int page_size, float scale, int window, int block, cudaStream_t stream) {
+                                   int page_size, float scale, int window, int block, const float* sink, cudaStream_t stream) {
   SLLM_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_mma: bad head counts nq=%d nkv=%d", nq, nkv);
   SLLM_REQUIRE(sllm_attention_mma_supports(hd), "attention_mma: head_dim=%d is not one of 16, 32, 64, 128", hd);
   SLLM_REQUIRE(page_size > 0 && max_pages > 0 && tiles >= 0 && total_tokens >= 0, "attention_mma: bad sizes");
@@ -430,6 +435,7 @@ SLLM_EXPORT int sllm_attention_mma(const void* q, const void* k_cache, const voi
   p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.window = window; p.block = block;
   p.num_splits = num_splits; p.total_tokens = total_tokens;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.sink = sink;
 #define DISPATCH(HD_)                                                             \
   case HD_:                                                                       \
     return decode ? launch_attention<HD_, true>(p, tiles, stream) : launch_attention<HD_, false>(p, tiles, stream);

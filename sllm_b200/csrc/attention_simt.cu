@@ -9,6 +9,7 @@
 //   maximum subtracted, o = sum p_j v_j   (ref/qwen3_5.py:373-390; one row:
 //   ref/incremental.py:75-87; kernels/cuda/kernels.cu:957-1025 for one CTA per head).
 //   Query head h reads kv head h / (nq / nkv) (ref/standard.py:65-68).
+//   With `sink` (one number per query head) the softmax's denominator also holds exp(sink_h).
 //
 // Each of the block's warps takes keys w, w+W, w+2W, ... in ascending order with an
 // online softmax; the warps' partial results are merged in warp order.  The order
@@ -28,7 +29,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
                       const int* __restrict__ block_tables, int max_pages, const int* __restrict__ positions,
                       const int* __restrict__ seq_of_token, int nq, int nkv, int hd, int page_size, float scale,
-                      int window, int chunk, TQ* __restrict__ out) {
+                      int window, int chunk, const float* __restrict__ sink, TQ* __restrict__ out) {
   __shared__ float qs[ATT_MAX_HD];
   __shared__ float acc_s[ATT_WARPS][ATT_MAX_HD];
   __shared__ float m_s[ATT_WARPS], l_s[ATT_WARPS];
@@ -85,6 +86,7 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
     f[w] = l_s[w] > 0.f ? expf(m_s[w] - mm) : 0.f;
     ll += l_s[w] * f[w];
   }
+  if (sink != nullptr) ll += expf(sink[h] - mm);       // a term of the denominator without key or value, not scaled
   const float inv = ll > 0.f ? 1.0f / ll : 0.f;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float o = 0.f;
@@ -101,7 +103,7 @@ using namespace sllm;
 SLLM_EXPORT int sllm_attention_simt(const void* q, const void* k_cache, const void* v_cache, int dtype,
                                     const int* block_tables, int max_pages, const int* positions,
                                     const int* seq_of_token, int T, int nq, int nkv, int hd, int page_size,
-                                    float scale, int window, int chunk, void* out, cudaStream_t stream) {
+                                    float scale, int window, int chunk, const float* sink, void* out, cudaStream_t stream) {
   SLLM_REQUIRE(T >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention: bad head counts nq=%d nkv=%d", nq, nkv);
   SLLM_REQUIRE(hd > 0 && hd <= ATT_MAX_HD, "attention: head_dim=%d is outside 1..%d", hd, ATT_MAX_HD);
   SLLM_REQUIRE(page_size > 0 && max_pages > 0, "attention: bad page_size=%d max_pages=%d", page_size, max_pages);
@@ -111,11 +113,11 @@ SLLM_EXPORT int sllm_attention_simt(const void* q, const void* k_cache, const vo
   if (dtype == SLLM_F32)
     launch_kernel(attention_simt_kernel<float, float>, grid, ATT_WARPS * 32, 0, stream,
         (const float*)q, (const float*)k_cache, (const float*)v_cache, block_tables, max_pages, positions,
-        seq_of_token, nq, nkv, hd, page_size, scale, window, chunk, (float*)out);
+        seq_of_token, nq, nkv, hd, page_size, scale, window, chunk, sink, (float*)out);
   else if (dtype == SLLM_BF16)
     launch_kernel(attention_simt_kernel<__nv_bfloat16, __nv_bfloat16>, grid, ATT_WARPS * 32, 0, stream,
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_tables,
-        max_pages, positions, seq_of_token, nq, nkv, hd, page_size, scale, window, chunk, (__nv_bfloat16*)out);
+        max_pages, positions, seq_of_token, nq, nkv, hd, page_size, scale, window, chunk, sink, (__nv_bfloat16*)out);
   else
     SLLM_REQUIRE(false, "attention: unknown dtype %d", dtype);
   return launch_status("attention_simt");

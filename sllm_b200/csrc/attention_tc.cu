@@ -77,6 +77,7 @@ struct AttnTcParams {
   int num_splits, tiles_per_split, total_tokens;
   float* part_o;
   float* part_lse;
+  const float* sink;             // [nq] or null: exp(sink_h) joins the softmax's denominator (no key, no value, not scaled)
 };
 
 constexpr int TC_BM = 128, TC_BN = 64;
@@ -497,6 +498,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       p.part_lse[(size_t)blockIdx.z * p.total_tokens * p.nq + orow] = (my_tiles > 0 && l > 0.f) ? m_used + log2f(l) : -INFINITY;
     if (ok && my_tiles > 0) {
       tc_fence_after();
+      if (p.sink != nullptr && p.num_splits == 1 && valid) l += exp2f(p.sink[kvh * G + row % G] * 1.4426950408889634f - m_used);
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* po = nullptr;
       if (valid) po = p.out + orow * HD;
@@ -535,7 +537,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 // The ranges' results of one (token, head) row merged: weights 2^(lse - max lse), ranges without a key skipped.
 template <int HD>
 __global__ void attention_tc_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
-                                            __nv_bfloat16* __restrict__ out, int rows, int num_splits) {
+                                            __nv_bfloat16* __restrict__ out, int rows, int num_splits, int nq,
+                                            const float* __restrict__ sink) {
   pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
   pdl_wait();
   const int row = blockIdx.x;
@@ -547,6 +550,7 @@ __global__ void attention_tc_combine_kernel(const float* __restrict__ part_o, co
     const float l = part_lse[(size_t)s * rows + row];
     tot += l == -INFINITY ? 0.f : exp2f(l - mt);
   }
+  if (sink != nullptr) tot += exp2f(sink[row % nq] * 1.4426950408889634f - mt);
   const float inv = tot > 0.f ? 1.f / tot : 0.f;
   for (int d = threadIdx.x; d < HD; d += blockDim.x) {
     float acc = 0.f;
@@ -611,7 +615,7 @@ static int launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const CUtenso
   int rc = launch_status("attention_tc");
   if (rc != SLLM_OK || p.num_splits == 1) return rc;
   launch_kernel(attention_tc_combine_kernel<HD>, p.total_tokens * p.nq, HD >= 128 ? 128 : 64, 0, stream,
-                (const float*)p.part_o, (const float*)p.part_lse, p.out, p.total_tokens * p.nq, p.num_splits);
+                (const float*)p.part_o, (const float*)p.part_lse, p.out, p.total_tokens * p.nq, p.num_splits, p.nq, p.sink);
   return launch_status("attention_tc_combine");
 }
 
@@ -636,8 +640,8 @@ SLLM_EXPORT int sllm_attention_tc(const void* q, const void* k_cache, const void
                                   const int* block_tables, int max_pages, const int* q_start, const int* ctx_len,
                                   const int* tile_seq, const int* tile_row0, int tiles, int row_tiles, int nq, int nkv,
                                   int hd, int page_size, float scale, int num_splits, int tiles_per_split, int total_tokens,
-                                  float* part_o, float* part_lse, const int* seq_row, const int* page_shift, int* status,
-                                  cudaStream_t stream) {
+                                  float* part_o, float* part_lse, const int* seq_row, const int* page_shift, const float* sink,
+                                  int* status, cudaStream_t stream) {
   SLLM_REQUIRE((seq_row == nullptr) == (page_shift == nullptr), "attention_tc: parts of requests need both their row and their first page");
   SLLM_REQUIRE(row_tiles == 1 || row_tiles == 2, "attention_tc: row_tiles=%d must be 1 or 2", row_tiles);
   SLLM_REQUIRE(num_splits >= 1 && num_splits <= 65535 && tiles_per_split >= 1, "attention_tc: bad context split %d x %d",
@@ -667,6 +671,7 @@ SLLM_EXPORT int sllm_attention_tc(const void* q, const void* k_cache, const void
   p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.scale_log2 = scale * 1.4426950408889634f;
   p.num_splits = num_splits; p.tiles_per_split = num_splits == 1 ? (1 << 30) / TC_BN : tiles_per_split;
   p.total_tokens = total_tokens; p.part_o = part_o; p.part_lse = part_lse; p.seq_row = seq_row; p.page_shift = page_shift;
+  p.sink = sink;
   if (row_tiles == 2)
     return hd == 128 ? launch_tc<128, 2>(mk, mv, rk, rv, p, tiles, stream) : launch_tc<64, 2>(mk, mv, rk, rv, p, tiles, stream);
   return hd == 128 ? launch_tc<128, 1>(mk, mv, rk, rv, p, tiles, stream) : launch_tc<64, 1>(mk, mv, rk, rv, p, tiles, stream);

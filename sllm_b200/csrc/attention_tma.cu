@@ -50,6 +50,7 @@ struct AttnTmaParams {
   int block;     // > 0: a query sees only keys of its own block of this many positions (counted from 0)
   int page_runs;                 // the run maps are valid: a tile of pages with consecutive ids is fetched as one box
   float scale_log2;
+  const float* sink;             // [nq] or null: exp(sink_h) joins the softmax's denominator (no key, no value, not scaled)
 };
 
 // Byte offset of the 16-byte chunk `chunk` (of the head's HD/8) of key row `row` within a stage's K or V.
@@ -382,6 +383,7 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
           const float4 v = *reinterpret_cast<const float4*>(mo + (w * 16 + r) * HD + d4);
           acc.x += v.x * f[w]; acc.y += v.y * f[w]; acc.z += v.z * f[w]; acc.w += v.w * f[w];
         }
+        if (p.sink != nullptr && p.num_splits == 1) lt += exp2f(p.sink[kvh * G + row % G] * 1.4426950408889634f - mt);
         const float inv = lt > 0.f ? 1.f / lt : 0.f;
         const size_t orow = (size_t)(q0 + row / G) * p.nq + kvh * G + row % G;
         if (p.num_splits > 1) {
@@ -410,7 +412,8 @@ constexpr int TA_MERGE_WARPS = 8;      // at most
 template <int HD>
 __global__ void attention_tma_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                              __nv_bfloat16* __restrict__ out, int rows, int num_splits,
-                                             const int* __restrict__ tile_seq, const int* __restrict__ q_start, int nq) {
+                                             const int* __restrict__ tile_seq, const int* __restrict__ q_start, int nq,
+                                             const float* __restrict__ sink) {
   // One CTA per (tile, query head, token of the tile's request): the rows the decode form wrote and no others, so
   // that a step's other rows (a prompt portion's, the prefill form's) are neither read nor touched.  The step's
   // description is read before the wait for the kernel before.  The ranges' weights are found by the threads side
@@ -452,6 +455,7 @@ __global__ void attention_tma_combine_kernel(const float* __restrict__ part_o, c
   __syncthreads();
   tot = red[1][0];
   for (int i = 1; i < warps; ++i) tot += red[1][i];
+  if (sink != nullptr) tot += exp2f(sink[blockIdx.y] * 1.4426950408889634f - mt);
   const float inv = tot > 0.f ? 1.f / tot : 0.f;
   // a warp takes every warps-th range, its lanes the row's columns in pairs; then the warps' sums are added
   float2 acc[VEC];
@@ -542,7 +546,7 @@ static int launch_ta(const CUtensorMap& mk, const CUtensorMap& mv, const CUtenso
     const int merge_warps = p.num_splits < TA_MERGE_WARPS ? (p.num_splits > 2 ? p.num_splits : 2) : TA_MERGE_WARPS;
     launch_kernel(attention_tma_combine_kernel<HD>, dim3((unsigned)tiles, (unsigned)p.nq, (unsigned)(16 / G > 0 ? 16 / G : 1)),
                   32 * merge_warps, 0, stream, (const float*)p.part_o, (const float*)p.part_lse, p.out, p.total_tokens * p.nq,
-                  p.num_splits, p.tile_seq, p.q_start, p.nq);
+                  p.num_splits, p.tile_seq, p.q_start, p.nq, p.sink);
     rc = launch_status("attention_tma_combine");
   }
   return rc;
@@ -571,8 +575,8 @@ SLLM_EXPORT int sllm_attention_tma_decode(const void* q, const void* k_cache, co
                                           void* out, float* part_o, float* part_lse, const int* block_tables,
                                           int max_pages, const int* q_start, const int* ctx_len, const int* tile_seq,
                                           const int* tile_row0, int tiles, int num_splits, int total_tokens, int nq,
-                                          int nkv, int hd, int page_size, float scale, int window, int block, int* status,
-                                          cudaStream_t stream) {
+                                          int nkv, int hd, int page_size, float scale, int window, int block, const float* sink,
+                                          int* status, cudaStream_t stream) {
   SLLM_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_tma: bad head counts nq=%d nkv=%d", nq, nkv);
   SLLM_REQUIRE(sllm_attention_tma_supports(hd, page_size), "attention_tma: head_dim=%d page_size=%d not taken", hd, page_size);
   SLLM_REQUIRE(max_pages > 0 && tiles >= 0 && total_tokens >= 0 && num_pages > 0, "attention_tma: bad sizes");
@@ -598,6 +602,7 @@ SLLM_EXPORT int sllm_attention_tma_decode(const void* q, const void* k_cache, co
   p.block_tables = block_tables; p.q_start = q_start; p.ctx_len = ctx_len; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
   p.status = status; p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.window = window; p.block = block;
   p.num_splits = num_splits; p.total_tokens = total_tokens; p.scale_log2 = scale * 1.4426950408889634f;
+  p.sink = sink;
 
   return hd == 128 ? launch_ta<128>(mk, mv, rk, rv, p, tiles, stream) : launch_ta<64>(mk, mv, rk, rv, p, tiles, stream);
 }

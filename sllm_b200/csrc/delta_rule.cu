@@ -30,6 +30,8 @@
 //       heads may share one query/key head (head h reads key head h / hdiv).
 //   gated linear attention (mode 2):  S <- diag(alpha) S + k v^T;  o = S^T (q r_scale),  alpha = sigmoid(z)^(1/tau) per key
 //       channel: u = a*u = 0, d = alpha; the walk's form for this mode has no sum before the update.
+//   linear attention with one fixed decay per head (mode 3):  S <- decay_h S + k v^T;  o = S^T q  with q, k and v each
+//       through silu first: mode 2's walk with d = decay_h on every row.
 //
 // A second kernel finishes the mixer's output: each head's o over its root mean square, times a gain,
 // times sigmoid(gate logit), in the compute dtype.
@@ -102,7 +104,7 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
         const bool in = tok && i < dk;
         k[q][m] = in ? __ldg(row + p.off_k + kh * dk + i) : 0.f;
         a[q][m] = (in && p.mode == 0) ? __ldg(row + p.off_a + h * dk + i) + __ldg(p.a_bias + h * dk + i) : 0.f;
-        d[q][m] = (in && p.mode != 1) ? __ldg(dec + i) : 0.f;
+        d[q][m] = (in && (p.mode == 0 || p.mode == 2)) ? __ldg(dec + i) : 0.f;
         r[q][m] = in ? __ldg(row + p.off_r + kh * dk + i) : 0.f;
       }
 #pragma unroll
@@ -158,6 +160,19 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
           s_u[tt * DKP] = g;
           s_u[tt * DKP + 1] = beta * g;
         }
+      } else if (p.mode == 3) {
+        const float dh = __ldg(p.a_log + h);           // the head's fixed decay
+#pragma unroll
+        for (int m = 0; m < PER_LANE; ++m) {
+          const int i = lane + 32 * m;
+          if (i < DKP) {
+            s_k[tt * DKP + i] = k[q][m] * sigmoidf_(k[q][m]);
+            s_d[tt * DKP + i] = i < dk ? dh : 0.f;
+            s_r[tt * DKP + i] = r[q][m] * sigmoidf_(r[q][m]);
+          }
+        }
+#pragma unroll
+        for (int m = 0; m < VPL; ++m) v[q][m] *= sigmoidf_(v[q][m]);
       } else {
 #pragma unroll
         for (int m = 0; m < PER_LANE; ++m) {
@@ -460,6 +475,24 @@ SLLM_EXPORT int sllm_gated_linear_attention(const float* proj, int ld, int off_q
   p.chunk = 1; p.max_q = max_q;
   p.mode = 2; p.hdiv = 1; p.gates = nullptr; p.ldg = p.off_b = p.off_dt = 0; p.a_log = p.dt_bias = nullptr;
   p.r_scale = q_scale; p.inv_tau = inv_tau;
+  return dispatch_delta_rule(p, S, stream);
+}
+
+// Linear attention with a fixed decay per head (`decay` [H]) over silu'd q | k | v columns of `proj` [T, ld].
+SLLM_EXPORT int sllm_decay_linear_attention(const float* proj, int ld, int off_q, int off_k, int off_v, const float* decay,
+                                            float* state, const int* q_start, const int* state_slots, float* out, int S, int H,
+                                            int dk, int dv, int max_q, cudaStream_t stream) {
+  SLLM_REQUIRE(S >= 0 && H > 0 && H <= 65535, "decay_linear_attention: bad sizes S=%d H=%d", S, H);
+  SLLM_REQUIRE(sllm_delta_rule_supports(dk, dv), "decay_linear_attention: a head of %d key and %d value channels is outside 1..256 keys", dk, dv);
+  SLLM_REQUIRE(off_q >= 0 && off_k >= 0 && off_v >= 0 && off_q + H * dk <= ld && off_k + H * dk <= ld && off_v + H * dv <= ld,
+               "decay_linear_attention: columns outside the product's %d", ld);
+  if (S == 0) return SLLM_OK;
+  DeltaParams p;
+  p.proj = proj; p.decay = proj; p.a_bias = nullptr; p.state = state; p.q_start = q_start; p.state_slots = state_slots;
+  p.out = out; p.ld = ld; p.off_r = off_q; p.off_k = off_k; p.off_v = off_v; p.off_a = 0; p.H = H; p.dk = dk; p.dv = dv;
+  p.chunk = 1; p.max_q = max_q;
+  p.mode = 3; p.hdiv = 1; p.gates = nullptr; p.ldg = p.off_b = p.off_dt = 0; p.a_log = decay; p.dt_bias = nullptr;
+  p.r_scale = 1.f; p.inv_tau = 1.f;
   return dispatch_delta_rule(p, S, stream);
 }
 

@@ -14,9 +14,13 @@
 
 namespace sllm {
 
+// With `tail` > 0 the `tail` columns after the latent are one more key part that every head shares: not normed, its first
+// `rot` channels rotated by position (rotate-half layout), written behind the latent; rows of the cache are D wide,
+// zeros beyond rank + tail.
 template <typename TC>
 __global__ void latent_write_kernel(const float* __restrict__ proj, int ld, int off, int rank, const float* __restrict__ gain,
-                                    float eps, const int* __restrict__ slot_mapping, TC* __restrict__ cache) {
+                                    float eps, const int* __restrict__ slot_mapping, TC* __restrict__ cache, int D, int tail,
+                                    int rot, const int* __restrict__ positions, const float* __restrict__ table, int max_pos) {
   __shared__ float red[33];
   pdl_launch_dependents();
   pdl_wait();
@@ -28,8 +32,21 @@ __global__ void latent_write_kernel(const float* __restrict__ proj, int ld, int 
   const float total = block_sum(ss, red);
   if (slot < 0) return;               // a row that pads the batch: no place to write to
   const float inv = 1.0f / sqrtf(total / (float)rank + eps);
-  TC* dst = cache + (size_t)slot * rank;
+  TC* dst = cache + (size_t)slot * D;
   for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = from_f32<TC>(x[i] * inv * gain[i]);
+  const float* y = x + rank;
+  const int half = rot / 2;
+  if (half > 0) {
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float* cs = table + (size_t)pos * rot;                    // cos[half] then sin[half]
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+      const float u = y[j], v = y[j + half], c = cs[j], sn = cs[half + j];
+      dst[rank + j] = from_f32<TC>(u * c - v * sn);
+      dst[rank + j + half] = from_f32<TC>(v * c + u * sn);
+    }
+  }
+  for (int d = rank + rot + threadIdx.x; d < D; d += blockDim.x) dst[d] = from_f32<TC>(d < rank + tail ? y[d - rank] : 0.f);
 }
 
 constexpr int HL_BM = 64, HL_BN = 64, HL_BK = 16;
@@ -37,7 +54,8 @@ constexpr int HL_BM = 64, HL_BN = 64, HL_BK = 16;
 template <typename TX, typename TW, typename TO>
 __global__ void __launch_bounds__(256)
 head_linear_kernel(const TX* __restrict__ x, int ldx, int xoff, const TW* __restrict__ w, TO* __restrict__ out,
-                   const float* __restrict__ gate, int ldg, int goff, int T, int H, int din, int dout) {
+                   const float* __restrict__ gate, int ldg, int goff, int T, int H, int din, int dout, int xstride, int ldo,
+                   int ostride, int gate_elem) {
   __shared__ float Xs[HL_BK][HL_BM + 4];
   __shared__ float Ws[HL_BK][HL_BN + 4];
   pdl_wait();
@@ -45,7 +63,7 @@ head_linear_kernel(const TX* __restrict__ x, int ldx, int xoff, const TW* __rest
   const int m0 = blockIdx.y * HL_BM, n0 = blockIdx.x * HL_BN;
   const int tid = threadIdx.x, tx = tid % 16, ty = tid / 16;
   const int lr = tid / 4, lk = (tid % 4) * 4;
-  const TX* xh = x + xoff + (size_t)h * din;
+  const TX* xh = x + xoff + (size_t)h * xstride;
   const TW* wh = w + (size_t)h * dout * din;
   float acc[4][4];
 #pragma unroll
@@ -82,11 +100,13 @@ head_linear_kernel(const TX* __restrict__ x, int ldx, int xoff, const TW* __rest
   for (int i = 0; i < 4; ++i) {
     const int m = m0 + ty * 4 + i;
     if (m >= T) continue;
-    const float g = gate != nullptr ? 1.0f / (1.0f + expf(-gate[(size_t)m * ldg + goff + h])) : 1.0f;
+    const float g = (gate != nullptr && !gate_elem) ? 1.0f / (1.0f + expf(-gate[(size_t)m * ldg + goff + h])) : 1.0f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
-      if (n < dout) out[(size_t)m * H * dout + (size_t)h * dout + n] = from_f32<TO>(acc[i][j] * g);
+      if (n >= dout) continue;
+      const float ge = (gate != nullptr && gate_elem) ? 1.0f / (1.0f + expf(-gate[(size_t)m * ldg + goff + (size_t)h * dout + n])) : g;
+      out[(size_t)m * ldo + (size_t)h * ostride + n] = from_f32<TO>(acc[i][j] * ge);
     }
   }
 }
@@ -101,13 +121,13 @@ template <typename TX>
 __global__ void __launch_bounds__(128)
 head_linear_mma_kernel(const TX* __restrict__ x, int ldx, int xoff, const __nv_bfloat16* __restrict__ w,
                        __nv_bfloat16* __restrict__ out, const float* __restrict__ gate, int ldg, int goff, int T, int H,
-                       int din, int dout, int vec) {
+                       int din, int dout, int vec, int xstride, int ldo, int ostride, int gate_elem) {
   __shared__ __align__(16) __nv_bfloat16 Xs[HM_BM][HM_LD];
   __shared__ __align__(16) __nv_bfloat16 Ws[HM_BN][HM_LD];
   pdl_wait();
   const int h = blockIdx.z, m0 = blockIdx.y * HM_BM, n0 = blockIdx.x * HM_BN;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
-  const TX* xh = x + xoff + (size_t)h * din;
+  const TX* xh = x + xoff + (size_t)h * xstride;
   const __nv_bfloat16* wh = w + (size_t)h * dout * din;
   float acc[8][4];
 #pragma unroll
@@ -168,13 +188,14 @@ head_linear_mma_kernel(const TX* __restrict__ x, int ldx, int xoff, const __nv_b
   for (int half = 0; half < 2; ++half) {
     const int m = m0 + warp * 16 + g + half * 8;
     if (m >= T) continue;
-    const float gt = gate != nullptr ? 1.0f / (1.0f + expf(-gate[(size_t)m * ldg + goff + h])) : 1.0f;
-    __nv_bfloat16* o = out + (size_t)m * H * dout + (size_t)h * dout;
+    const float gt = (gate != nullptr && !gate_elem) ? 1.0f / (1.0f + expf(-gate[(size_t)m * ldg + goff + h])) : 1.0f;
+    const float* ge = (gate != nullptr && gate_elem) ? gate + (size_t)m * ldg + goff + (size_t)h * dout : nullptr;
+    __nv_bfloat16* o = out + (size_t)m * ldo + (size_t)h * ostride;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int n = n0 + j * 8 + 2 * t4;
-      if (n < dout) o[n] = __float2bfloat16_rn(acc[j][half * 2] * gt);
-      if (n + 1 < dout) o[n + 1] = __float2bfloat16_rn(acc[j][half * 2 + 1] * gt);
+      if (n < dout) o[n] = __float2bfloat16_rn(acc[j][half * 2] * (ge ? 1.0f / (1.0f + expf(-ge[n])) : gt));
+      if (n + 1 < dout) o[n + 1] = __float2bfloat16_rn(acc[j][half * 2 + 1] * (ge ? 1.0f / (1.0f + expf(-ge[n + 1])) : gt));
     }
   }
 }
@@ -183,46 +204,69 @@ head_linear_mma_kernel(const TX* __restrict__ x, int ldx, int xoff, const __nv_b
 
 using namespace sllm;
 
-SLLM_EXPORT int sllm_latent_write(const float* proj, int ld, int off, int rank, const float* gain, float eps,
-                                  const int* slot_mapping, void* cache, int cache_dtype, int T, cudaStream_t stream) {
-  SLLM_REQUIRE(T >= 0 && rank > 0 && off >= 0 && off + rank <= ld, "latent_write: columns %d..%d of %d", off, off + rank, ld);
+SLLM_EXPORT int sllm_latent_rope_write(const float* proj, int ld, int off, int rank, int tail, int rot, const float* gain, float eps,
+                                       const int* positions, const float* table, int max_pos, const int* slot_mapping, void* cache,
+                                       int cache_dtype, int D, int T, cudaStream_t stream) {
+  SLLM_REQUIRE(T >= 0 && rank > 0 && tail >= 0 && off >= 0 && off + rank + tail <= ld, "latent_write: columns %d..%d of %d", off,
+               off + rank + tail, ld);
+  SLLM_REQUIRE(D >= rank + tail, "latent_write: rows of %d do not hold %d + %d", D, rank, tail);
+  SLLM_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= tail, "latent_write: %d rotated channels of %d", rot, tail);
+  SLLM_REQUIRE(rot == 0 || (positions != nullptr && table != nullptr && max_pos > 0), "latent_write: rotary table missing");
   if (T == 0) return SLLM_OK;
   const int threads = rank >= 512 ? 256 : 128;
   if (cache_dtype == SLLM_F32)
-    launch_kernel(latent_write_kernel<float>, T, threads, 0, stream, proj, ld, off, rank, gain, eps, slot_mapping, (float*)cache);
+    launch_kernel(latent_write_kernel<float>, T, threads, 0, stream, proj, ld, off, rank, gain, eps, slot_mapping, (float*)cache, D,
+                  tail, rot, positions, table, max_pos);
   else if (cache_dtype == SLLM_BF16)
     launch_kernel(latent_write_kernel<__nv_bfloat16>, T, threads, 0, stream, proj, ld, off, rank, gain, eps, slot_mapping,
-                  (__nv_bfloat16*)cache);
+                  (__nv_bfloat16*)cache, D, tail, rot, positions, table, max_pos);
   else
     SLLM_REQUIRE(false, "latent_write: unknown dtype %d", cache_dtype);
   return launch_status("latent_write");
 }
 
-SLLM_EXPORT int sllm_head_linear(const void* x, int x_dtype, int ldx, int xoff, const void* w, int w_dtype, void* out, int out_dtype,
-                                 const float* gate, int ldg, int goff, int T, int H, int din, int dout, cudaStream_t stream) {
+SLLM_EXPORT int sllm_latent_write(const float* proj, int ld, int off, int rank, const float* gain, float eps,
+                                  const int* slot_mapping, void* cache, int cache_dtype, int T, cudaStream_t stream) {
+  return sllm_latent_rope_write(proj, ld, off, rank, 0, 0, gain, eps, nullptr, nullptr, 0, slot_mapping, cache, cache_dtype, rank, T,
+                                stream);
+}
+
+// Heads `xstride` apart in x (>= din) and `ostride` apart in rows of `ldo` of the output (>= dout; what lies between is
+// left as it is).  gate_elem 0: one gate logit per (token, head); 1: one per output element, at goff + h*dout + n.
+SLLM_EXPORT int sllm_head_linear_strided(const void* x, int x_dtype, int ldx, int xoff, int xstride, const void* w, int w_dtype,
+                                         void* out, int out_dtype, int ldo, int ostride, const float* gate, int ldg, int goff,
+                                         int gate_elem, int T, int H, int din, int dout, cudaStream_t stream) {
   SLLM_REQUIRE(T >= 0 && H > 0 && H <= 65535 && din > 0 && dout > 0, "head_linear: bad sizes T=%d H=%d din=%d dout=%d", T, H, din, dout);
-  SLLM_REQUIRE(xoff >= 0 && xoff + H * din <= ldx, "head_linear: columns %d..%d of %d", xoff, xoff + H * din, ldx);
-  SLLM_REQUIRE(gate == nullptr || (goff >= 0 && goff + H <= ldg), "head_linear: gate columns outside %d", ldg);
+  SLLM_REQUIRE(xstride >= din && xoff >= 0 && xoff + (long)(H - 1) * xstride + din <= ldx, "head_linear: columns %d.. of %d", xoff, ldx);
+  SLLM_REQUIRE(ostride >= dout && (long)(H - 1) * ostride + dout <= ldo, "head_linear: %d heads of %d do not fit rows of %d", H, ostride, ldo);
+  SLLM_REQUIRE(gate == nullptr || (goff >= 0 && goff + (gate_elem ? (long)H * dout : (long)H) <= ldg), "head_linear: gate columns outside %d", ldg);
   if (T == 0) return SLLM_OK;
   const dim3 grid((unsigned)((dout + HL_BN - 1) / HL_BN), (unsigned)((T + HL_BM - 1) / HL_BM), (unsigned)H);
   SLLM_REQUIRE(grid.y <= 65535, "head_linear: too many rows for one launch");
 #define SLLM_HL(TX, TW, TO)                                                                                              \
   launch_kernel(head_linear_kernel<TX, TW, TO>, grid, 256, 0, stream, (const TX*)x, ldx, xoff, (const TW*)w, (TO*)out, gate, ldg, \
-                goff, T, H, din, dout)
+                goff, T, H, din, dout, xstride, ldo, ostride, gate_elem)
   if (w_dtype == SLLM_BF16 && out_dtype == SLLM_BF16 && (x_dtype == SLLM_F32 || x_dtype == SLLM_BF16)) {
     // the bfloat16 path: tensor cores; 16-byte loads where every row of x and of W starts on a 16-byte boundary
     const int xe = x_dtype == SLLM_F32 ? 4 : 8;
-    const int vec = din % 8 == 0 && ldx % xe == 0 && xoff % xe == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0;
+    const int vec = din % 8 == 0 && ldx % xe == 0 && xoff % xe == 0 && xstride % xe == 0 && ((uintptr_t)x & 15) == 0 &&
+                    ((uintptr_t)w & 15) == 0;
     if (x_dtype == SLLM_F32)
       launch_kernel(head_linear_mma_kernel<float>, grid, 128, 0, stream, (const float*)x, ldx, xoff, (const __nv_bfloat16*)w,
-                    (__nv_bfloat16*)out, gate, ldg, goff, T, H, din, dout, vec);
+                    (__nv_bfloat16*)out, gate, ldg, goff, T, H, din, dout, vec, xstride, ldo, ostride, gate_elem);
     else
       launch_kernel(head_linear_mma_kernel<__nv_bfloat16>, grid, 128, 0, stream, (const __nv_bfloat16*)x, ldx, xoff,
-                    (const __nv_bfloat16*)w, (__nv_bfloat16*)out, gate, ldg, goff, T, H, din, dout, vec);
+                    (const __nv_bfloat16*)w, (__nv_bfloat16*)out, gate, ldg, goff, T, H, din, dout, vec, xstride, ldo, ostride, gate_elem);
     return launch_status("head_linear");
   }
   if (x_dtype == SLLM_F32 && w_dtype == SLLM_F32 && out_dtype == SLLM_F32) SLLM_HL(float, float, float);
   else SLLM_REQUIRE(false, "head_linear: dtypes x=%d w=%d out=%d", x_dtype, w_dtype, out_dtype);
 #undef SLLM_HL
   return launch_status("head_linear");
+}
+
+SLLM_EXPORT int sllm_head_linear(const void* x, int x_dtype, int ldx, int xoff, const void* w, int w_dtype, void* out, int out_dtype,
+                                 const float* gate, int ldg, int goff, int T, int H, int din, int dout, cudaStream_t stream) {
+  return sllm_head_linear_strided(x, x_dtype, ldx, xoff, din, w, w_dtype, out, out_dtype, H * dout, dout, gate, ldg, goff, 0, T, H, din,
+                                  dout, stream);
 }

@@ -70,11 +70,13 @@ qk_norm_rope_kv_write_kernel(const float* __restrict__ qkv, int ld, const float*
   for (int d = rot + lane; d < D; d += 32) dst[d] = from_f32<TC>(d < dim ? x[d] * inv * gain[d] : 0.f);
 }
 
-// grid (T, ceil(C / 256)): a thread per (token, channel)
+// grid (T, ceil(C / 256)): a thread per (token, channel).  MODE 0: silu of the convolution; MODE 1: the input plus its
+// convolution (a convolution in front of a sublayer that keeps the sublayer's input as it was beside it).
+template <int MODE, typename TO>
 __global__ void __launch_bounds__(256)
-short_conv_silu_kernel(const float* __restrict__ x, int ld, int off, const float* __restrict__ w, int taps,
-                       const float* __restrict__ state, const int* __restrict__ seq_of_token, const int* __restrict__ q_start,
-                       const int* __restrict__ state_slots, float* __restrict__ out, int C) {
+short_conv_kernel(const float* __restrict__ x, int ld, int off, const float* __restrict__ w, int taps,
+                  const float* __restrict__ state, const int* __restrict__ seq_of_token, const int* __restrict__ q_start,
+                  const int* __restrict__ state_slots, TO* __restrict__ out, int C) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -83,13 +85,14 @@ short_conv_silu_kernel(const float* __restrict__ x, int ld, int off, const float
   const int first = q_start[seq];
   const float* st = state + ((size_t)state_slots[seq] * C + c) * (taps - 1);
   const float* wc = w + (size_t)c * taps;
-  float acc = 0.f;
+  float acc = 0.f, now = 0.f;
   for (int j = taps - 1; j >= 0; --j) {                 // oldest input first: one order whatever the cut
     const int src = t - j;
     const float v = src >= first ? x[(size_t)src * ld + off + c] : st[taps - 1 - (first - src)];
     acc = fmaf(wc[taps - 1 - j], v, acc);
+    now = v;
   }
-  out[(size_t)t * C + c] = sbs_silu(acc);
+  out[(size_t)t * C + c] = from_f32<TO>(MODE == 0 ? sbs_silu(acc) : now + acc);
 }
 
 // grid (S, ceil(C / 256)): a thread per (request, channel) rewrites its state row in ascending order
@@ -156,19 +159,36 @@ SLLM_EXPORT int sllm_qk_norm_rope_kv_write(const float* qkv, int ld, const float
   return launch_status("qk_norm_rope_kv_write");
 }
 
-SLLM_EXPORT int sllm_short_conv_silu(const float* x, int ld, int off, const float* w, int taps, float* state,
-                                     const int* seq_of_token, const int* q_start, const int* state_slots, float* out, int T,
-                                     int S, int C, cudaStream_t stream) {
+// mode 0: silu(conv(x)), float32 out; mode 1: x + conv(x) in `out_dtype`.  The state rows are rewritten by a second launch.
+SLLM_EXPORT int sllm_short_conv(const float* x, int ld, int off, const float* w, int taps, float* state, const int* seq_of_token,
+                                const int* q_start, const int* state_slots, void* out, int out_dtype, int mode, int T, int S, int C,
+                                cudaStream_t stream) {
   SLLM_REQUIRE(T >= 0 && S >= 0 && C > 0 && taps >= 1 && off >= 0 && off + C <= ld, "short_conv: bad sizes T=%d C=%d taps=%d", T, C, taps);
   SLLM_REQUIRE(taps == 1 || state != nullptr, "short_conv: a convolution over %d taps needs its state", taps);
+  SLLM_REQUIRE((mode == 0 && out_dtype == SLLM_F32) || (mode == 1 && (out_dtype == SLLM_F32 || out_dtype == SLLM_BF16)),
+               "short_conv: mode %d with output dtype %d", mode, out_dtype);
   if (T == 0) return SLLM_OK;
   const unsigned cb = (unsigned)((C + 255) / 256);
-  launch_kernel(short_conv_silu_kernel, dim3((unsigned)T, cb), 256, 0, stream, x, ld, off, w, taps, (const float*)state,
-                seq_of_token, q_start, state_slots, out, C);
-  int rc = launch_status("short_conv_silu");
+  const dim3 grid((unsigned)T, cb);
+  if (mode == 0)
+    launch_kernel(short_conv_kernel<0, float>, grid, 256, 0, stream, x, ld, off, w, taps, (const float*)state, seq_of_token, q_start,
+                  state_slots, (float*)out, C);
+  else if (out_dtype == SLLM_F32)
+    launch_kernel(short_conv_kernel<1, float>, grid, 256, 0, stream, x, ld, off, w, taps, (const float*)state, seq_of_token, q_start,
+                  state_slots, (float*)out, C);
+  else
+    launch_kernel(short_conv_kernel<1, __nv_bfloat16>, grid, 256, 0, stream, x, ld, off, w, taps, (const float*)state, seq_of_token,
+                  q_start, state_slots, (__nv_bfloat16*)out, C);
+  int rc = launch_status("short_conv");
   if (rc != SLLM_OK || taps == 1 || S == 0) return rc;
   launch_kernel(short_conv_state_kernel, dim3((unsigned)S, cb), 256, 0, stream, x, ld, off, taps, state, q_start, state_slots, C);
   return launch_status("short_conv_state");
+}
+
+SLLM_EXPORT int sllm_short_conv_silu(const float* x, int ld, int off, const float* w, int taps, float* state,
+                                     const int* seq_of_token, const int* q_start, const int* state_slots, float* out, int T,
+                                     int S, int C, cudaStream_t stream) {
+  return sllm_short_conv(x, ld, off, w, taps, state, seq_of_token, q_start, state_slots, out, SLLM_F32, 0, T, S, C, stream);
 }
 
 SLLM_EXPORT int sllm_norm_mean_add(float* stream_, const float* a, const float* ga, const float* b, const float* gb, float eps,

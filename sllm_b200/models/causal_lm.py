@@ -11,9 +11,10 @@ from .. import ops
 from ..config.plan import ModelPlan
 from ..parts import delta_rule as _delta_rule, experts as _experts, latent_attention as _latent  # noqa: F401
 from ..parts import linear_attention as _linear_attention, parallel as _parallel, side_by_side as _side_by_side  # noqa: F401
+from ..parts import gated_recurrence as _gated_recurrence, sandwich as _sandwich  # noqa: F401
 from ..parts import standard as _standard  # noqa: F401  (each import registers its parts)
 from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, SHIFTS,
-                          LayerCache, OwedNorm, StepContext, TensorSpec, join_name)
+                          LayerCache, OwedNorm, SlotState, StepContext, TensorSpec, flatten_needs, join_name)
 
 
 FAMILIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "shift": SHIFTS}
@@ -104,7 +105,9 @@ class CausalLM:
         out = []
         for e in self.plan.run_list:
             if e.cache_from is not None:
-                out.append(("borrow", e.cache_from))
+                # the pages are borrowed; what the layer keeps per request beside them (a convolution's last inputs) is its own
+                own = tuple(n for n in flatten_needs(self.layers[e.layer].cache_need()) if isinstance(n, SlotState))
+                out.append(("borrow", e.cache_from, own) if own else ("borrow", e.cache_from))
             else:
                 out.append(("own", self.layers[e.layer].cache_need()))
         return out

@@ -281,6 +281,24 @@ def qk_norm_rope_kv_write(qkv, q_gain, k_gain, eps: float, positions, table, rot
     return q
 
 
+def short_conv_add(x, weight, state, step, out_dtype) -> torch.Tensor:
+    """``x + conv(x)``: the float32 rows ``x [T, C]`` plus their causal convolution over time per channel (``weight`` float32
+    ``[C, taps]``, the current token's tap last; the inputs before a request's portion from its row of ``state`` ``[slots, C,
+    taps-1]``, which then receives the portion's last ones), in ``out_dtype``."""
+    _chk(x, weight, state)
+    T, C = x.shape
+    taps = weight.shape[1]
+    if x.dtype != torch.float32 or weight.dtype != torch.float32 or tuple(weight.shape) != (C, taps) or \
+            (taps > 1 and tuple(state.shape[1:]) != (C, taps - 1)):
+        raise KernelError("short_conv_add: float32 input and taps [C, taps], and a state [slots, C, taps-1]")
+    out = torch.empty((T, C), dtype=out_dtype, device=x.device)
+    call("sllm_short_conv", _p(x), C, 0, _p(weight), taps, _p(state) if taps > 1 else None, _p(step.seq_of_token), _p(step.q_start),
+         _p(step.state_slots), _p(out), _dtc(out_dtype), 1, T, step.num_seqs, C, _stream())
+    if taps > 1:
+        launches["own"] += 1          # the state's kernel
+    return out
+
+
 def short_conv_silu(x, off: int, weight, state, step) -> torch.Tensor:
     """``silu`` of a causal convolution over time, per channel, of columns ``off .. off+C`` of the float32 product ``x``:
     ``weight`` float32 ``[C, taps]`` with the current token's tap last; the ``taps - 1`` inputs before a request's portion
@@ -338,7 +356,115 @@ def moe_act(up, dense, ff: int, out_dtype) -> torch.Tensor:
     return out
 
 
+def moe_route_top_softmax(logits, top: int):
+    """The ``top`` largest of the float32 router logits ``[T, E]`` win (the lower index on a tie); their weights are the
+    softmax over the winners alone.  (dense weights float32 ``[T, E]`` with zeros elsewhere, indices int32 ``[T, top]`` by
+    falling logit, weights float32 ``[T, top]``)."""
+    _chk(logits)
+    T, E = logits.shape
+    if logits.dtype != torch.float32:
+        raise KernelError("moe_route_top_softmax: the router's logits are float32")
+    dense = torch.empty((T, E), dtype=torch.float32, device=logits.device)
+    idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    wts = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    call("sllm_moe_route_top_softmax", _p(logits), T, E, int(top), _p(dense), _p(idx), _p(wts), _stream())
+    return dense, idx, wts
+
+
+def gated_clamp_act(gu, interleave: int, limit: float, out_dtype, *, alpha: float = 1.702, dense=None, ff: int | None = None):
+    """``g' sigmoid(alpha g') (u' + 1)`` with ``g' = min(g, limit)`` and ``u' = clamp(u, -limit, limit)`` of ``gu [T, 2N]``
+    whose columns alternate between gate and up in blocks of ``interleave``.  With ``dense`` (float32 ``[T, E]``, the
+    routing weights of E experts of ``ff`` columns each, N = E ff): also times the token's weight of the column's expert;
+    the columns of an expert a token does not use are not read."""
+    _chk(gu, dense)
+    T, two_n = gu.shape
+    N = two_n // 2
+    E = dense.shape[1] if dense is not None else 0
+    out = torch.empty((T, N), dtype=out_dtype, device=gu.device)
+    call("sllm_gated_clamp_act", _p(gu), _dt(gu), _p(dense), _p(out), _dtc(out_dtype), T, N, E, int(ff if dense is not None else N),
+         int(interleave), float(limit), float(alpha), _stream())
+    return out
+
+
+# ---- sublayers between two norms; an element-wise gated recurrence ---------------------------------------------------
+
+def post_add_norm(stream, term, post_gain, post_eps: float, pre_gain, pre_eps: float, out_dtype=torch.float32):
+    """``stream += term / rms(term) * post_gain`` (skipped when ``term`` is None; ``term`` float32 ``[T, W]`` or a stack of
+    partial sums ``[parts, T, W]``), then ``stream / rms(stream) * pre_gain`` in ``out_dtype`` (None when ``pre_gain`` is
+    None).  Gains float32 ``[W]``; everything float32."""
+    _chk(stream, term, post_gain, pre_gain)
+    T, W = stream.shape
+    if stream.dtype != torch.float32 or (term is not None and tuple(term.shape[-2:]) != (T, W)):
+        raise KernelError("post_add_norm: a float32 stream [T, W] and a term that fits it")
+    h = torch.empty((T, W), dtype=out_dtype, device=stream.device) if pre_gain is not None else None
+    call("sllm_post_add_norm", _p(stream), *_term(term), _p(post_gain), float(post_eps), _p(pre_gain), float(pre_eps), _p(h),
+         _dtc(out_dtype), T, W, _stream())
+    return h
+
+
+def mingru_scan(proj, offs, state, step, width: int, out_dtype) -> torch.Tensor:
+    """``S <- (1 - z) S + z c`` element by element over the step's tokens, request by request in token order, from and into
+    ``state`` (float32 ``[slots, width]``), with z = sigmoid(a), c = b + 1/2 where b >= 0 and sigmoid(b) elsewhere, read out
+    as ``S * silu(g)``; a, b, g are the float32 columns ``offs = (a, b, g)`` of ``proj [T, ld]``.  ``[T, width]``."""
+    _chk(proj, state)
+    T, ld = proj.shape
+    if proj.dtype != torch.float32 or state.dtype != torch.float32 or tuple(state.shape[1:]) != (width,):
+        raise KernelError("mingru_scan: a float32 product and a state [slots, width]")
+    out = torch.empty((T, width), dtype=out_dtype, device=proj.device)
+    oz, ox, og = (int(o) for o in offs)
+    call("sllm_mingru_scan", _p(proj), ld, oz, ox, og, _p(state), _p(step.q_start), _p(step.state_slots), _p(out), _dtc(out_dtype),
+         step.num_seqs, int(width), _stream())
+    return out
+
+
+def decay_linear_attention(proj, offs, decay, state, step, heads: int, dk: int, dv: int) -> torch.Tensor:
+    """S <- decay_h S + k v^T; o = S^T q with q, k, v each through silu, over the step's tokens from and into ``state``
+    (float32 ``[slots, heads, dk, dv]``).  ``proj`` float32 ``[T, ld]`` holds q, k, v at columns ``offs``; ``decay`` float32
+    ``[heads]``.  Returns ``o`` float32 ``[T, heads*dv]``."""
+    _chk(proj, decay, state)
+    T, ld = proj.shape
+    if proj.dtype != torch.float32 or decay.dtype != torch.float32 or state.dtype != torch.float32:
+        raise KernelError("decay_linear_attention: everything that enters the recurrence is float32")
+    if tuple(decay.shape) != (heads,) or tuple(state.shape[1:]) != (heads, dk, dv):
+        raise KernelError(f"decay_linear_attention: decay {tuple(decay.shape)} or state {tuple(state.shape)} does not fit {heads} heads of {dk}x{dv}")
+    out = torch.empty((T, heads * dv), dtype=torch.float32, device=proj.device)
+    off_q, off_k, off_v = (int(o) for o in offs)
+    call("sllm_decay_linear_attention", _p(proj), ld, off_q, off_k, off_v, _p(decay), _p(state), _p(step.q_start),
+         _p(step.state_slots), _p(out), step.num_seqs, heads, dk, dv, int(step.max_q_len), _stream())
+    return out
+
+
 # ---- latent attention ------------------------------------------------------------------------------------
+
+def latent_rope_write(proj, off: int, rank: int, tail: int, rotary_dim: int, gain, eps: float, positions, table, slot_mapping,
+                      cache) -> None:
+    """`latent_write` with ``tail`` more columns behind the latent: a key part all heads share, not normed, its first
+    ``rotary_dim`` channels rotated by position (``table`` float32 ``[positions, 2, rotary_dim/2]``).  Rows of the cache
+    ``[pages, 1, page_size, D]`` receive latent, tail and zeros up to D."""
+    _chk(proj, gain, positions, table, slot_mapping, cache)
+    D = cache.shape[3]
+    if proj.dtype != torch.float32 or cache.shape[1] != 1 or D < rank + tail:
+        raise KernelError("latent_rope_write: a float32 product and a cache [pages, 1, page_size, D >= rank + tail]")
+    max_pos = 0
+    if rotary_dim:
+        if table is None or table.dtype != torch.float32 or tuple(table.shape[1:]) != (2, rotary_dim // 2):
+            raise KernelError("latent_rope_write: rotary table must be float32 [positions, 2, rotary_dim/2]")
+        max_pos = table.shape[0]
+    call("sllm_latent_rope_write", _p(proj), proj.shape[1], int(off), int(rank), int(tail), int(rotary_dim), _p(gain), float(eps),
+         _p(positions), _p(table), max_pos, _p(slot_mapping), _p(cache), _dt(cache), D, proj.shape[0], _stream())
+
+
+def rope_cols_(out, ooff: int, ostride: int, x, xoff: int, xstride: int, n: int, rotary_dim: int, positions, table, heads: int) -> None:
+    """Per head h: the ``n`` columns ``x[t, xoff + h*xstride ..]`` of a float32 product, the first ``rotary_dim`` of them
+    rotated by position, written to ``out[t, h*ostride + ooff ..]``; what lies between ``ooff + n`` and the head's next
+    ``ostride`` is zeroed."""
+    _chk(out, x, positions, table)
+    if x.dtype != torch.float32:
+        raise KernelError("rope_cols_: a float32 product")
+    max_pos = table.shape[0] if rotary_dim else 0
+    call("sllm_rope_cols", _p(x), x.shape[1], int(xoff), int(xstride), int(n), int(rotary_dim), _p(positions), _p(table), max_pos,
+         _p(out), _dt(out), out.shape[1], int(ooff), int(ostride), x.shape[0], int(heads), _stream())
+
 
 def latent_write(proj, off: int, rank: int, gain, eps: float, slot_mapping, cache) -> None:
     """Columns ``off .. off+rank`` of the float32 product, over their root mean square, times ``gain``: each
@@ -351,15 +477,19 @@ def latent_write(proj, off: int, rank: int, gain, eps: float, slot_mapping, cach
          _dt(cache), proj.shape[0], _stream())
 
 
-def head_linear(x, xoff: int, w, out_dtype, *, gate=None, goff: int = 0) -> torch.Tensor:
-    """A product per head: ``out[t, h, :] = w[h] @ x[t, xoff + h*din : xoff + (h+1)*din]`` with ``w [H, dout, din]``,
-    times ``sigmoid(gate[t, goff + h])`` if ``gate`` (a float32 product) is given.  ``[T, H*dout]`` in ``out_dtype``."""
+def head_linear(x, xoff: int, w, out_dtype, *, gate=None, goff: int = 0, gate_elem: bool = False, xstride: int | None = None,
+                ostride: int | None = None) -> torch.Tensor:
+    """A product per head: ``out[t, h, :] = w[h] @ x[t, xoff + h*xstride : .. + din]`` with ``w [H, dout, din]`` (heads
+    ``xstride`` apart in x, ``din`` by default), times ``sigmoid(gate[t, goff + h])`` if ``gate`` (a float32 product) is
+    given, or, with ``gate_elem``, times ``sigmoid(gate[t, goff + h*dout + n])`` element by element.  ``[T, H*ostride]`` in
+    ``out_dtype`` (``ostride`` >= dout, dout by default; the columns between are left for the caller to fill)."""
     _chk(x, w, gate)
     T, ldx = x.shape
     H, dout, din = w.shape
-    out = torch.empty((T, H * dout), dtype=out_dtype, device=x.device)
-    call("sllm_head_linear", _p(x), _dt(x), ldx, int(xoff), _p(w), _dt(w), _p(out), _dtc(out_dtype), _p(gate),
-         gate.shape[1] if gate is not None else 0, int(goff), T, H, din, dout, _stream())
+    xs, os_ = int(xstride or din), int(ostride or dout)
+    out = torch.empty((T, H * os_), dtype=out_dtype, device=x.device)
+    call("sllm_head_linear_strided", _p(x), _dt(x), ldx, int(xoff), xs, _p(w), _dt(w), _p(out), _dtc(out_dtype), H * os_, os_,
+         _p(gate), gate.shape[1] if gate is not None else 0, int(goff), 1 if gate_elem else 0, T, H, din, dout, _stream())
     return out
 
 
@@ -1053,8 +1183,9 @@ def rope_kv_write(qkv, bias, positions, table, rotary_dim, nq, nkv, hd, slot_map
     return q
 
 
-def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, nq, nkv, hd, scale, window, block=None):
-    """The CUDA-core attention kernel: any head size up to 256, float32 arithmetic."""
+def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, nq, nkv, hd, scale, window, block=None, sink=None):
+    """The CUDA-core attention kernel: any head size up to 256, float32 arithmetic.  ``sink`` (float32 ``[nq]``): the
+    softmax's denominator also holds exp(sink_h), a term without key or value that the scale does not touch."""
     _chk(q, k_cache, v_cache, block_tables, positions, seq_of_token)
     T = q.shape[0]
     if q.dtype != k_cache.dtype:
@@ -1063,7 +1194,7 @@ def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, n
     out = torch.empty_like(q)
     call("sllm_attention_simt", _p(q), _p(k_cache), _p(v_cache), _dt(q), _p(block_tables),
          block_tables.shape[1], _p(positions), _p(seq_of_token), T, nq, nkv, hd, page_size, float(scale),
-         int(window or 0), int(block or 0), _p(out), _stream())
+         int(window or 0), int(block or 0), _p(sink), _p(out), _stream())
     return out
 
 
@@ -1137,7 +1268,7 @@ def choose_splits(num_small: int, nkv: int, max_ctx: int, ctas_per_sm: int = 2, 
 
 
 def attention_mma(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, decode: bool, num_splits: int,
-                  nq, nkv, hd, scale, window, out=None, block=None):
+                  nq, nkv, hd, scale, window, out=None, block=None, sink=None):
     """The tensor-core attention kernel on one tile list (see `attention_tiles`); the merge of a split context
     touches the rows of that list's requests only."""
     _chk(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles[0], tiles[1])
@@ -1152,7 +1283,7 @@ def attention_mma(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, de
         part_lse = torch.empty((num_splits, T, nq), dtype=torch.float32, device=q.device)
     call("sllm_attention_mma", _p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_o), _p(part_lse), _p(block_tables),
          block_tables.shape[1], _p(q_start), _p(ctx_len), _p(tiles[0]), _p(tiles[1]), tiles[2], 1 if decode else 0,
-         num_splits, T, nq, nkv, hd, k_cache.shape[2], float(scale), int(window or 0), int(block or 0), _stream())
+         num_splits, T, nq, nkv, hd, k_cache.shape[2], float(scale), int(window or 0), int(block or 0), _p(sink), _stream())
     if num_splits > 1:
         launches["own"] += 1          # the combine kernel
     return out
@@ -1169,7 +1300,7 @@ def _tma_ctas_per_sm(hd: int) -> int:
 
 
 def attention_tma_decode(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, num_splits: int,
-                         nq, nkv, hd, scale, window, out=None, block=None):
+                         nq, nkv, hd, scale, window, out=None, block=None, sink=None):
     """The decode form fed by TMA (16-row tiles only; see `attention_tiles`)."""
     _chk(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles[0], tiles[1])
     if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
@@ -1184,7 +1315,7 @@ def attention_tma_decode(q, k_cache, v_cache, block_tables, q_start, ctx_len, ti
     call("sllm_attention_tma_decode", _p(q), _p(k_cache), _p(v_cache), k_cache.shape[0], _p(out), _p(part_o),
          _p(part_lse), _p(block_tables), block_tables.shape[1], _p(q_start), _p(ctx_len), _p(tiles[0]), _p(tiles[1]),
          tiles[2], num_splits, T, nq, nkv, hd, k_cache.shape[2], float(scale), int(window or 0), int(block or 0),
-         _p(_status_word(q.device)), _stream())
+         _p(sink), _p(_status_word(q.device)), _stream())
     _tc_used["since_check"] += 1
     if num_splits > 1:
         launches["own"] += 1
@@ -1220,7 +1351,7 @@ def choose_tc_splits(num_tiles: int, nkv: int, max_ctx: int) -> tuple[int, int]:
 
 
 def attention_tc(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, nq, nkv, hd, scale, out=None,
-                 row_tiles: int = 1, splits: tuple[int, int] = (1, 0), parts=None):
+                 row_tiles: int = 1, splits: tuple[int, int] = (1, 0), parts=None, sink=None):
     """The prefill form on tcgen05 (tiles of 128 * row_tiles rows, row_tiles 1 or 2; no window; see
     `attention_tiles`).  ``splits`` = (ranges, 64-key tiles a range) cuts the context into ranges
     that run as CTAs of their own and are merged afterwards; ranges x tiles must cover the longest
@@ -1241,7 +1372,7 @@ def attention_tc(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, nq,
     call("sllm_attention_tc", _p(q), _p(k_cache), _p(v_cache), k_cache.shape[0], _p(out), _p(block_tables),
          block_tables.shape[1], _p(q_start), _p(ctx_len), _p(tiles[0]), _p(tiles[1]), tiles[2], int(row_tiles), nq, nkv,
          hd, k_cache.shape[2], float(scale), n_splits, max(per, 1), T, _p(part_o), _p(part_lse),
-         _p(parts[0]) if parts else None, _p(parts[1]) if parts else None, _p(_status_word(q.device)), _stream())
+         _p(parts[0]) if parts else None, _p(parts[1]) if parts else None, _p(sink), _p(_status_word(q.device)), _stream())
     if n_splits > 1:
         launches["own"] += 1               # the merge kernel
     _tc_used["since_check"] += 1
@@ -1287,8 +1418,9 @@ def mma_supports(hd: int) -> bool:
     return bool(lib().sllm_attention_mma_supports(int(hd)))
 
 
-def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, window, block=None):
-    """Causal attention of the step's tokens over their requests' pages.  ``window``: only the last ``window`` keys;
+def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, window, block=None, sink=None):
+    """Causal attention of the step's tokens over their requests' pages.  ``sink`` (float32 ``[nq]``): exp(sink_h) joins
+    each head's softmax denominator (every form takes it).  ``window``: only the last ``window`` keys;
     ``block``: only the keys of the query's own block of ``block`` positions, counted from the sequence's start (both
     run on the mma.sync and TMA-fed forms, not on tcgen05).  bfloat16 with a head size
     the tensor-core kernels take: requests of at most 16 (token, head-in-group) rows go to the decode
@@ -1298,7 +1430,7 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
     g = step.groups[group]
     if q.dtype != torch.bfloat16 or not mma_supports(hd):
         return attention_simt(q, k_cache, v_cache, g.block_tables, step.positions, step.seq_of_token,
-                              nq, nkv, hd, scale, window, block)
+                              nq, nkv, hd, scale, window, block, sink)
     G = nq // nkv
     # blocks that start on page borders: the prefill form runs each block's part of a portion as a causal sequence of its own
     blocked_tc = bool(block) and block % k_cache.shape[2] == 0 and bool(step.ctx_lens)
@@ -1326,19 +1458,19 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
     out = torch.empty_like(q)
     if small and tma_attention_supports(hd, k_cache.shape[2]):
         attention_tma_decode(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, small, splits,
-                             nq, nkv, hd, scale, window, out, block)
+                             nq, nkv, hd, scale, window, out, block, sink)
     elif small:
         attention_mma(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, small, True, splits,
-                      nq, nkv, hd, scale, window, out, block)
+                      nq, nkv, hd, scale, window, out, block, sink)
     if large and use_tc and parts is not None:
         attention_tc(q, k_cache, v_cache, g.block_tables, parts[0], parts[1], parts[3], nq, nkv, hd, scale, out,
-                     row_tiles=rows // 128, parts=parts[2])
+                     row_tiles=rows // 128, parts=parts[2], sink=sink)
     elif large and use_tc:
         attention_tc(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, large, nq, nkv, hd, scale, out,
-                     row_tiles=rows // 128, splits=tc_splits)
+                     row_tiles=rows // 128, splits=tc_splits, sink=sink)
     elif large:
         attention_mma(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, large, False, 1,
-                      nq, nkv, hd, scale, window, out, block)
+                      nq, nkv, hd, scale, window, out, block, sink)
     return out
 
 

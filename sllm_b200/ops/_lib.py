@@ -74,7 +74,7 @@ def _declare(L):
                                c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "sllm_gemm_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "sllm_attention_simt": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
-                                c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
+                                c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "sllm_sample_rows": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "sllm_repetition_penalty": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "sllm_mark_seen": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
@@ -84,12 +84,12 @@ def _declare(L):
         "sllm_attention_tma_ctas_per_sm": [c_int],
         "sllm_attention_tma_decode": [c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                      c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
+                                      c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "sllm_wait_probe": [c_void_p, ctypes.c_ulonglong, c_void_p, c_void_p],
         "sllm_attention_tc_supports": [c_int, c_int],
         "sllm_attention_tc": [c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
-                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "sllm_gemm_tcgen05_supports": [c_int, c_int, c_int],
         "sllm_gemm_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "sllm_gemm_pair_supports": [c_int, c_int, c_int],
@@ -117,7 +117,24 @@ def _declare(L):
                                c_int, c_void_p],
         "sllm_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                               c_int, c_int, c_float, c_int, c_int, c_void_p],
+                               c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
+        "sllm_post_add_norm": [c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_float, c_void_p, c_float, c_void_p, c_int, c_int,
+                               c_int, c_void_p],
+        "sllm_mingru_scan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                             c_void_p],
+        "sllm_gated_clamp_act": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                                 c_void_p],
+        "sllm_moe_route_top_softmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+        "sllm_rope_cols": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                           c_int, c_int, c_int, c_void_p],
+        "sllm_short_conv": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                            c_int, c_int, c_int, c_void_p],
+        "sllm_decay_linear_attention": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "sllm_latent_rope_write": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int,
+                                   c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "sllm_head_linear_strided": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
+                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     }
     for name, argtypes in sigs.items():
         fn = getattr(L, name)

@@ -71,3 +71,62 @@ class RoutedExperts(FeedForward):
 
     def weight_bytes(self):
         return self.up.nbytes() + self.down.nbytes() + self.router.nbytes() + 4 * self.E
+
+
+@FEED_FORWARDS.register("gated_experts")
+class GatedExperts(FeedForward):
+    """A mixture of gated experts behind a router that takes the largest logits:
+
+        z = W_router x (float32);  the ``top`` largest z win;  their weights are the softmax over the winners alone
+        expert e:  g = min(W_gate,e x, limit),  u = clamp(W_up,e x, -limit, limit),  W_down,e (g sigmoid(alpha g) (u + 1))
+        out = sum over the winners of weight_e * expert_e(x)
+
+    Parameters: ``hidden_size``, ``experts``, ``top``, ``expert_ff``, ``limit``, ``alpha`` (1.702 unless given); no biases.  As
+    in `RoutedExperts`, all experts' gate and up projections are ONE matrix (expert e's rows at 2 e ff, gate and up rows
+    alternating in blocks of 8, or all of the expert's gate rows before its up rows where ff is no multiple of 8) and their
+    down projections one matrix side by side; a token's activation row carries its routing weights, so the second product
+    adds up the weighted experts in float32 in one order whatever the batch holds."""
+
+    def __init__(self, params, **kw):
+        super().__init__(params, **kw)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.E, self.top = int(p["experts"]), int(p["top"])
+        self.ff = int(p["expert_ff"])
+        self.limit, self.alpha = float(p["limit"]), float(p.get("alpha", 1.702))
+        self.interleave = 8 if self.ff % 8 == 0 else self.ff
+        if not 1 <= self.top <= self.E:
+            raise ValueError(f"gated_experts: top={self.top} of {self.E} experts cannot be chosen")
+
+    def tensor_specs(self):
+        W = self.hidden
+        specs = []
+        for e in range(self.E):
+            specs += [TensorSpec(f"e{e}.gate", (self.ff, W)), TensorSpec(f"e{e}.up", (self.ff, W)), TensorSpec(f"e{e}.down", (W, self.ff))]
+        specs.append(TensorSpec("router", (self.E, W)))
+        return specs
+
+    def bind(self, fetch):
+        n, W = self.interleave, self.hidden
+        rows = []
+        for e in range(self.E):
+            g, u = fetch(f"e{e}.gate").reshape(self.ff // n, n, W), fetch(f"e{e}.up").reshape(self.ff // n, n, W)
+            rows.append(torch.stack([g, u], dim=1).reshape(2 * self.ff, W))
+        self.gate_up = Linear(self._matrix(torch.cat(rows, dim=0)))                                          # [2 E ff, W]
+        self.down = Linear(self._matrix(torch.cat([fetch(f"e{e}.down") for e in range(self.E)], dim=1)))     # [W, E ff]
+        self.router = Linear(self._matrix(fetch("router")))
+
+    accepts_residual = True
+
+    def route(self, x):
+        """(dense weights [T, E], indices [T, top], weights [T, top]) of the normed rows ``x``."""
+        return ops.moe_route_top_softmax(self.router(x, torch.float32), self.top)
+
+    def forward(self, x, step, residual=None):
+        dense, _, _ = self.route(x)
+        gu = self.gate_up(x, self.dtype)                                                                     # [T, 2 E ff]
+        act = ops.gated_clamp_act(gu, self.interleave, self.limit, self.dtype, alpha=self.alpha, dense=dense, ff=self.ff)
+        return self.down.into(act, residual)
+
+    def weight_bytes(self):
+        return self.gate_up.nbytes() + self.down.nbytes() + self.router.nbytes()

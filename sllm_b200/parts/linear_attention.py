@@ -80,3 +80,62 @@ class GatedLinearAttention(Mixer):
 
     def weight_bytes(self):
         return self.inp.nbytes() + self.a1.nbytes() + self.a2.nbytes() + self.out.nbytes() + 4 * self.gain.numel()
+
+
+@MIXERS.register("decay_linear_attention")
+class DecayLinearAttention(Mixer):
+    """Linear attention with ONE fixed decay per head:
+
+        S_t = decay_h S_(t-1) + k_t v_t^T,        o_t = S_t^T q_t,        q, k, v = silu of their projections
+
+    (no other scale).  The heads' outputs together, over their common root mean square, times a gain of ``heads * vdim``
+    numbers, times sigmoid(W_g x), then W_o.  Parameters: ``hidden_size``, ``heads``, ``dim``, ``vdim``, ``decay`` (one number
+    per head), ``eps`` (of the output's norm).  q, k, v and the gate are one matrix whose product stays float32."""
+
+    NAMES = ("q", "k", "v", "g")
+
+    def __init__(self, params, **kw):
+        super().__init__(params, **kw)
+        self.hidden = int(params["hidden_size"])
+        self.heads = int(params["heads"])
+        self.dim = int(params["dim"])
+        self.vdim = int(params["vdim"])
+        self.eps = float(params["eps"])
+        decay = [float(d) for d in params["decay"]]
+        if len(decay) != self.heads:
+            raise ValueError(f"decay_linear_attention: {len(decay)} decays for {self.heads} heads")
+        if not ops.delta_rule_supports(self.dim, self.vdim):
+            raise ValueError(f"decay_linear_attention: a head of {self.dim} key channels is outside what the recurrence kernel "
+                             f"keeps in registers (1..256)")
+        self.decay = torch.tensor(decay, dtype=torch.float32).to(self.device)
+
+    def cache_need(self):
+        return SlotState((self.heads, self.dim, self.vdim), "lightning")
+
+    def tensor_specs(self):
+        H, W = self.heads, self.hidden
+        K, V = H * self.dim, H * self.vdim
+        return [TensorSpec("q", (K, W)), TensorSpec("k", (K, W)), TensorSpec("v", (V, W)), TensorSpec("g", (V, W)),
+                TensorSpec("o", (W, V)), TensorSpec("norm", (V,), role="gain")]
+
+    def bind(self, fetch):
+        K, V = self.heads * self.dim, self.heads * self.vdim
+        self.inp = Linear(self._matrix(torch.cat([fetch(n) for n in self.NAMES], dim=0)))
+        self.offs = (0, K, 2 * K)
+        self.off_g = 2 * K + V
+        self.gain = self._f32(fetch("norm"))
+        self.out = Linear(self._matrix(fetch("o")))
+
+    accepts_residual = True
+
+    def mix(self, x, step: StepContext, cache: LayerCache, position=None, write_cache=True):
+        proj = self.inp(x, torch.float32)                                            # [T, 2K + 2V] float32
+        o = ops.decay_linear_attention(proj, self.offs, self.decay, cache.states["lightning"], step, self.heads, self.dim, self.vdim)
+        # one norm over all heads: the output kernel's "head" is the whole row
+        return ops.delta_out(o, self.gain, proj, self.off_g, self.eps, 1, self.heads * self.vdim, self.dtype, "sigmoid")
+
+    def forward(self, x, step, cache, position, write_cache=True, residual=None):
+        return self.out.into(self.mix(x, step, cache, position, write_cache), residual)
+
+    def weight_bytes(self):
+        return self.inp.nbytes() + self.out.nbytes() + 4 * self.gain.numel() + 4 * self.heads

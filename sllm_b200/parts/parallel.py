@@ -94,7 +94,9 @@ class Sinusoidal(PositionEncoding):
 @FEED_FORWARDS.register("gated_dense")
 class GatedDense(FeedForward):
     """down(act(gate(x)) * up(x)) with a bias on each of the three products (optional as a set) and ``act`` one of
-    ``gelu_tanh`` (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))) and ``silu``.  gate and up are one matrix whose rows
+    ``gelu_tanh`` (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))) and ``silu``; or, with ``activation`` =
+    ``clamped_swish``, down(g sigmoid(alpha g) (u + 1)) with g = min(gate(x), limit) and u = clamp(up(x), -limit, limit)
+    (``limit``; ``alpha``, 1.702 unless given).  gate and up are one matrix whose rows
     (and biases) alternate in blocks of 8, so that a tile of the product holds a gate row and its up row together and the
     activation can be applied where the tile is made (all gate rows first where the size is no multiple of 8)."""
 
@@ -107,8 +109,10 @@ class GatedDense(FeedForward):
         self.names = params.get("names", ("gate", "up", "down"))
         self.bias_suffix = params.get("bias_suffix", "b")
         self.interleave = 8 if self.inter % 8 == 0 else self.inter
-        if self.act not in ops.ACTIVATIONS:
-            raise ValueError(f"gated_dense: activation {self.act!r}; known: {sorted(ops.ACTIVATIONS)}")
+        if self.act not in ops.ACTIVATIONS and self.act != "clamped_swish":
+            raise ValueError(f"gated_dense: activation {self.act!r}; known: {sorted(ops.ACTIVATIONS) + ['clamped_swish']}")
+        if self.act == "clamped_swish":
+            self.limit, self.alpha = float(params["limit"]), float(params.get("alpha", 1.702))
         self.gate_up = None
         self.down = None
 
@@ -137,7 +141,11 @@ class GatedDense(FeedForward):
     accepts_residual = True
 
     def forward(self, x, step, residual=None):
-        act = ops.linear_act_mul(x, self.gate_up.weight, self.gate_up.bias, self.interleave, self.dtype, self.act)   # [T, I]
+        if self.act == "clamped_swish":
+            gu = ops.linear(x, self.gate_up.weight, self.gate_up.bias, self.dtype)                               # [T, 2I]
+            act = ops.gated_clamp_act(gu, self.interleave, self.limit, self.dtype, alpha=self.alpha)
+        else:
+            act = ops.linear_act_mul(x, self.gate_up.weight, self.gate_up.bias, self.interleave, self.dtype, self.act)   # [T, I]
         return self.down.into(act, residual)
 
     def weight_bytes(self):

@@ -241,14 +241,132 @@ def latent_write(proj, off, rank, gain, eps, slot_mapping, cache):
     cache[slots // ps, 0, slots % ps, :] = c[ok].to(cache.dtype)
 
 
-def head_linear(x, xoff, w, out_dtype, *, gate=None, goff=0):
+def head_linear(x, xoff, w, out_dtype, *, gate=None, goff=0, gate_elem=False, xstride=None, ostride=None):
     H, dout, din = w.shape
     T = x.shape[0]
-    xs = x[:, xoff:xoff + H * din].to(w.dtype).float().reshape(T, H, din)      # (operands in the matrix's dtype)
+    xs_, os_ = xstride or din, ostride or dout
+    xs = x[:, xoff:xoff + H * xs_].reshape(T, H, xs_)[:, :, :din].to(w.dtype).float()      # (operands in the matrix's dtype)
     out = torch.einsum("thi,hoi->tho", xs, w.float())
-    if gate is not None:
+    if gate is not None and gate_elem:
+        out = out * torch.sigmoid(gate[:, goff:goff + H * dout]).reshape(T, H, dout)
+    elif gate is not None:
         out = out * torch.sigmoid(gate[:, goff:goff + H])[:, :, None]
-    return out.reshape(T, H * dout).to(out_dtype)
+    full = torch.zeros((T, H, os_), dtype=out_dtype, device=x.device)
+    full[:, :, :dout] = out.to(out_dtype)
+    return full.reshape(T, H * os_)
+
+
+def _rotate(x, positions, table, rot):
+    """x [..., n]: the first ``rot`` channels in the rotate-half layout by ``table`` [positions, 2, rot/2]."""
+    if not rot:
+        return x
+    half = rot // 2
+    cs = table[positions.long()]                       # [T, 2, half]
+    shape = [x.shape[0]] + [1] * (x.dim() - 2) + [half]
+    c, sn = cs[:, 0].reshape(shape), cs[:, 1].reshape(shape)
+    u, v = x[..., :half], x[..., half:rot]
+    return torch.cat([u * c - v * sn, v * c + u * sn, x[..., rot:]], dim=-1)
+
+
+def latent_rope_write(proj, off, rank, tail, rotary_dim, gain, eps, positions, table, slot_mapping, cache):
+    x = proj[:, off:off + rank]
+    c = x * (x.pow(2).mean(-1, keepdim=True) + eps).rsqrt() * gain
+    row = torch.zeros((proj.shape[0], cache.shape[3]), dtype=torch.float32, device=proj.device)
+    row[:, :rank] = c
+    row[:, rank:rank + tail] = _rotate(proj[:, off + rank:off + rank + tail].float(), positions, table, rotary_dim)
+    ps = cache.shape[2]
+    ok = slot_mapping >= 0
+    slots = slot_mapping[ok].long()
+    cache[slots // ps, 0, slots % ps, :] = row[ok].to(cache.dtype)
+
+
+def rope_cols_(out, ooff, ostride, x, xoff, xstride, n, rotary_dim, positions, table, heads):
+    T = x.shape[0]
+    src = x[:, xoff:].float()
+    o = out.reshape(T, heads, ostride)
+    for h in range(heads):
+        o[:, h, ooff:ooff + n] = _rotate(src[:, h * xstride:h * xstride + n], positions, table, rotary_dim).to(out.dtype)
+        o[:, h, ooff + n:] = 0
+
+
+def short_conv_add(x, weight, state, step, out_dtype):
+    C, taps = weight.shape
+    out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+    starts = step.q_start.long().tolist()
+    for s in range(step.num_seqs):
+        a, b = starts[s], starts[s + 1]
+        slot = int(step.state_slots[s])
+        xs = x[a:b].float()
+        before = state[slot].t() if taps > 1 else xs[:0]                 # [taps-1, C], oldest first
+        padded = torch.cat([before, xs], dim=0)
+        acc = xs.clone()
+        for j in range(taps):
+            acc += padded[j:j + b - a] * weight[:, j]
+        out[a:b] = acc
+        if taps > 1:
+            state[slot] = padded[padded.shape[0] - (taps - 1):].t()
+    return out.to(out_dtype)
+
+
+def moe_route_top_softmax(logits, top):
+    T, E = logits.shape
+    idx = torch.sort(-logits.float(), dim=-1, stable=True).indices[:, :top]
+    wts = torch.softmax(logits.float().gather(1, idx), dim=-1)
+    dense = torch.zeros((T, E), dtype=torch.float32, device=logits.device)
+    dense.scatter_(1, idx, wts)
+    return dense, idx.int(), wts
+
+
+def gated_clamp_act(gu, interleave, limit, out_dtype, *, alpha=1.702, dense=None, ff=None):
+    T, two_n = gu.shape
+    N = two_n // 2
+    v = gu.float().reshape(T, N // interleave, 2, interleave)
+    g = v[:, :, 0, :].reshape(T, N).clamp(max=limit)
+    u = v[:, :, 1, :].reshape(T, N).clamp(-limit, limit)
+    y = g * torch.sigmoid(alpha * g) * (u + 1.0)
+    if dense is not None:
+        y = y * dense.repeat_interleave(ff, dim=1)
+    return y.to(out_dtype)
+
+
+def post_add_norm(stream, term, post_gain, post_eps, pre_gain, pre_eps, out_dtype=torch.float32):
+    if term is not None:
+        t = term.float().sum(0) if term.dim() == 3 else term.float()
+        stream += t * (t.pow(2).mean(-1, keepdim=True) + post_eps).rsqrt() * post_gain
+    if pre_gain is None:
+        return None
+    return (stream * (stream.pow(2).mean(-1, keepdim=True) + pre_eps).rsqrt() * pre_gain).to(out_dtype)
+
+
+def mingru_scan(proj, offs, state, step, width, out_dtype):
+    oz, ox, og = offs
+    z = torch.sigmoid(proj[:, oz:oz + width])
+    b = proj[:, ox:ox + width]
+    cand = torch.where(b >= 0, b + 0.5, torch.sigmoid(b))
+    g = proj[:, og:og + width]
+    out = torch.empty((proj.shape[0], width), dtype=torch.float32, device=proj.device)
+
+    def token(t, S):
+        S = (1.0 - z[t]) * S + z[t] * cand[t]
+        return S, S * g[t] * torch.sigmoid(g[t])
+    _walk(step, state, out, token)
+    return out.to(out_dtype)
+
+
+def decay_linear_attention(proj, offs, decay, state, step, heads, dk, dv):
+    T = proj.shape[0]
+    off_q, off_k, off_v = offs
+    act = torch.nn.functional.silu
+    q = act(proj[:, off_q:off_q + heads * dk]).reshape(T, heads, dk)
+    k = act(proj[:, off_k:off_k + heads * dk]).reshape(T, heads, dk)
+    v = act(proj[:, off_v:off_v + heads * dv]).reshape(T, heads, dv)
+    out = torch.empty((T, heads, dv), dtype=torch.float32, device=proj.device)
+
+    def token(t, S):
+        S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
+        return S, torch.einsum("hij,hi->hj", S, q[t])
+    _walk(step, state, out, token)
+    return out.reshape(T, heads * dv)
 
 
 def add_rmsnorm(residual, delta, weight, eps, out_dtype):
@@ -313,7 +431,7 @@ def rope_kv_write(qkv, bias, positions, table, rotary_dim, nq, nkv, hd, slot_map
     return q
 
 
-def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, nq, nkv, hd, scale, window, block=None):
+def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, nq, nkv, hd, scale, window, block=None, sink=None):
     T = q.shape[0]
     ps = k_cache.shape[2]
     out = torch.empty((T, nq, hd), dtype=torch.float32, device=q.device)
@@ -331,15 +449,18 @@ def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, n
         k = k.repeat_interleave(rep, dim=1)
         v = v.repeat_interleave(rep, dim=1)
         s = torch.einsum("hd,nhd->hn", qf[t], k) * scale
-        p = torch.softmax(s, dim=-1)
+        if sink is not None:                               # one more term of the denominator: no key, no value, not scaled
+            p = torch.softmax(torch.cat([s, sink.float()[:, None]], dim=-1), dim=-1)[:, :-1]
+        else:
+            p = torch.softmax(s, dim=-1)
         out[t] = torch.einsum("hn,nhd->hd", p, v)
     return out.reshape(T, nq * hd).to(q.dtype)
 
 
-def paged_attention(q, k_cache, v_cache, step, group, nq, nkv, hd, scale, window, block=None):
+def paged_attention(q, k_cache, v_cache, step, group, nq, nkv, hd, scale, window, block=None, sink=None):
     g = step.groups[group]
     return attention_simt(q, k_cache, v_cache, g.block_tables, step.positions, step.seq_of_token,
-                          nq, nkv, hd, scale, window, block)
+                          nq, nkv, hd, scale, window, block, sink)
 
 
 def gather_rows(x, rows):
@@ -388,7 +509,8 @@ def penalty_from_seen_(logits, seen, step, penalty):
     return logits
 
 
-ALL = ["gated_delta_rule", "gated_linear_attention", "qk_norm_rope_kv_write", "short_conv_silu", "norm_mean_add_", "moe_route", "moe_act",
+ALL = ["latent_rope_write", "rope_cols_", "short_conv_add", "moe_route_top_softmax", "gated_clamp_act", "post_add_norm", "mingru_scan",
+       "decay_linear_attention", "gated_delta_rule", "gated_linear_attention", "qk_norm_rope_kv_write", "short_conv_silu", "norm_mean_add_", "moe_route", "moe_act",
        "add_sinusoid_", "add_group_ssq", "group_norm_shift", "act_mul", "linear_act_mul", "tanh_cols", "delta_rule", "delta_out", "latent_write",
        "head_linear", "embed_gather", "add_rmsnorm", "linear", "can_accumulate", "linear_accumulate", "silu_mul", "linear_silu_mul", "rope_kv_write",
        "attention_simt", "paged_attention", "gather_rows", "sample_rows", "repetition_penalty_", "mark_seen", "penalty_from_seen_"]
