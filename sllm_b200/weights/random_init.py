@@ -43,7 +43,8 @@ def random_tensors(specs, seed: int, *, std: float = 0.02, bias_std: float | Non
             a = rng.uniform(0.05, 0.95, shape).astype(np.float32)
         else:
             a = std * rng.standard_normal(shape, dtype=np.float32)
-        out[s.name] = torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dt)
+        # (ascontiguousarray makes one dimension of none: a single number keeps its shape of no dimensions)
+        out[s.name] = torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).reshape(tuple(shape)).to(dt)
     return out
 
 

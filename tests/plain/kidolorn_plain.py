@@ -189,13 +189,18 @@ def dense(h, w, p, mlp):
 
 def route(h, w, p, r, margins=None):
     """(indices [T, top] by falling logit, weights [T, top]): the largest logits win, softmax over the winners only.
-    ``margins``: a list that receives, per token, the gap between the last winner and the first loser."""
+    ``margins``: a list that receives one array per call: per token, the gap between the last winner and the first loser
+    relative to the largest logit's size (infinite where every expert is chosen)."""
     z = h @ w[p + "router"].T
     order = np.argsort(-z, axis=-1, kind="stable")
     idx = order[:, :r["top"]]
     chosen = np.take_along_axis(z, idx, axis=-1)
-    if margins is not None and r["top"] < r["experts"]:
-        margins.extend((chosen[:, -1] - np.take_along_axis(z, order[:, r["top"]:r["top"] + 1], axis=-1)[:, 0]).tolist())
+    if margins is not None:
+        if r["top"] < r["experts"]:
+            gap = chosen[:, -1] - np.take_along_axis(z, order[:, r["top"]:r["top"] + 1], axis=-1)[:, 0]
+            margins.append(gap / (np.abs(z).max(-1) + 1e-30))
+        else:
+            margins.append(np.full(z.shape[0], np.inf))
     e = np.exp(chosen - chosen.max(-1, keepdims=True))
     return idx, e / e.sum(-1, keepdims=True)
 
