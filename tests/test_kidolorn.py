@@ -504,12 +504,15 @@ def test_latent_attention_and_a_second_layer_on_the_same_latents(dev, H, dk, dr,
         m.bind(lambda rel: torch.from_numpy(w["m." + rel].astype(np.float32)))
         return m
     w1, w2 = weights(H, dk, dv, True), weights(H2, dk2, dv2, False)
-    first, second = build(H, dk, dv, 0.21, w1, False), build(H2, dk2, dv2, 0.13, w2, True)
+    # scales that leave the scores a spread of about 3 and 1.5 (what the weights above give a score before it is scaled)
+    spread = lambda dk: 0.4 * np.sqrt(W) * np.sqrt(dk * 0.09 * rank + dr * 0.16 * W)
+    sc1, sc2 = float(np.float32(3.0 / spread(dk))), float(np.float32(1.5 / spread(dk2)))
+    first, second = build(H, dk, dv, sc1, w1, False), build(H2, dk2, dv2, sc2, w2, True)
     assert first.cache_need() == second.cache_need() and first.cache_need().head_dim >= rank + dr
     lens, slots = {0: 110, 1: 37}, {0: 0, 1: 1}
-    xs = {s: rng.standard_normal((n, W)) for s, n in lens.items()}
-    m1 = {"heads": H, "dim": dk, "rot_dim": dr, "vdim": dv, "kv_rank": rank, "scale": 0.21, "rot": {"base": base, "dims": dr}}
-    m2 = dict(m1, heads=H2, dim=dk2, vdim=dv2, scale=0.13)
+    xs = {s: _bf16_exact({"x": rng.standard_normal((n, W))})["x"] for s, n in lens.items()}
+    m1 = {"heads": H, "dim": dk, "rot_dim": dr, "vdim": dv, "kv_rank": rank, "scale": sc1, "rot": {"base": base, "dims": dr}}
+    m2 = dict(m1, heads=H2, dim=dk2, vdim=dv2, scale=sc2)
     want1, want2 = {}, {}
     for s, x in xs.items():
         lat = plain.latent_parts(x, w1, "m.", m1, eps, np.arange(len(x)))
@@ -525,14 +528,17 @@ def test_latent_attention_and_a_second_layer_on_the_same_latents(dev, H, dk, dr,
     def run(rows, step):
         slot_map = np.concatenate([[tables[row[s], p // ps] * ps + p % ps for p in range(a, b)] for s, a, b in rows]).astype(np.int32)
         step.groups = [GroupView(ps, torch.from_numpy(tables[[row[s] for s, _, _ in rows]]).to(dev), torch.from_numpy(slot_map).to(dev))]
-        x = to(np.concatenate([xs[s][a:b] for s, a, b in rows]))
+        x = to(np.concatenate([xs[s][a:b] for s, a, b in rows])).to(td)
         terms = [m.forward(x, step, cache, None) for m in (first, second)]
         return np.concatenate([(t.sum(0) if t.dim() == 3 else t).float().cpu().numpy() for t in terms], axis=1)
     got = _portions(dev, lens, slots, [(70, 1), (1, 2), (2, 9), (13, 1), (1, 1), (40, 40)], run)
-    tol = 5e-4 if dtype == "float32" else 4e-2
     for s in lens:
-        np.testing.assert_allclose(got[s][:, :W], want1[s], rtol=tol, atol=tol)
-        np.testing.assert_allclose(got[s][:, W:], want2[s], rtol=tol, atol=tol)
+        for g, want in ((got[s][:, :W], want1[s]), (got[s][:, W:], want2[s])):
+            if dtype == "float32":
+                np.testing.assert_allclose(g, want, rtol=5e-4, atol=5e-4)
+            else:       # bfloat16 products: a row's difference against the row's own size (a row that the sink all but empties: against a hundredth of the rows' common size)
+                e = np.sqrt(((g - want) ** 2).mean(-1)) / np.maximum(np.sqrt((want ** 2).mean(-1)), 0.01 * np.sqrt((want ** 2).mean()))
+                assert e.max() < 0.05 and np.quantile(e, 0.9) < 0.02, (s, float(e.max()), int(e.argmax()))
 
 
 @pytest.mark.parametrize("W,ff,limit,T", [(36, 20, 0.8, 41), (64, 72, 1.0, 9), (40, 17, 2.5, 30), (128, 256, 0.5, 70)])
@@ -700,7 +706,7 @@ def _sharp(t):
     tolerance."""
     for n in list(t):
         if n.endswith("mix.q") and n.replace("mix.q", "mix.sink") in t:
-            t[n] *= 5.0
+            t[n] *= 3.0
         if n.endswith("mix.sink"):
             t[n] = t[n] * 0 + torch.linspace(-4.0, 3.0, t[n].numel())
         if n.endswith("mix.z.b"):
