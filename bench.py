@@ -426,6 +426,35 @@ def nutopel_config(sz: dict) -> dict:
             "layers": [gla if i % 2 == 0 else pair for i in range(sz["layers"])]}
 
 
+def kidolorn_config(sz: dict) -> dict:
+    """Kidolorn at one size: the same width, depth and vocabulary; the layers go round four kinds: linear attention with a
+    fixed decay per head (heads of 64 x 64, the state of the other designs' recurrent heads) before a mixture of experts;
+    latent attention whose cached row is as wide as Rososun's latent (a latent of 96 and a rotated part of 32 beside the
+    other design's 128), a query head of 96 + 32 channels and a value head of 128, before a dense feed-forward; the
+    element-wise recurrence over the model's width before a mixture; a second latent attention that reads the first one's
+    cache, before a dense feed-forward.  The mixture is Nutopel's without its shared expert: eight experts of a quarter of
+    the dense size, two of them used.  Four taps of input convolution in front of every sublayer."""
+    W, H, D = sz["width"], sz["heads"], sz["dim"]
+    rot, rank = D // 4, sz["kv_rank"] - D // 4
+    moe = {"kind": "moe", "expert": {"ff": sz["ff"] // 4 // 64 * 64, "limit": 7.0}, "router": {"experts": 8, "top": 2}}
+    dense = {"kind": "dense", "ff": sz["ff"], "limit": 7.0}
+    heads = W // 64
+    decay = [1.0 - 2.0 ** (-5.0 - 5.0 * h / max(heads - 1, 1)) for h in range(heads)]
+    latent = {"heads": H, "dim": D - rot, "rot_dim": rot, "vdim": D, "kv_rank": rank, "scale": D ** -0.5, "rot": {"base": 10000.0, "dims": rot}}
+    layers = []
+    for i in range(sz["layers"]):
+        kind = i % 4
+        if kind == 0:
+            layers.append({"type": "lightning", "mixer": {"heads": heads, "dim": 64, "vdim": 64, "decay": decay}, "mlp": moe})
+        elif kind == 1:
+            layers.append({"type": "latent_attention", "mixer": dict(latent), "mlp": dense})
+        elif kind == 2:
+            layers.append({"type": "mingru", "mixer": {"width": W}, "mlp": moe})
+        else:
+            layers.append({"type": "latent_attention", "mixer": dict(latent, kv_from=i - 2), "mlp": dense})
+    return {"architecture": "Kidolorn", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "layers": layers}
+
+
 def design_run(args) -> dict:
     global PREFILL_TOKENS
     import torch
@@ -438,8 +467,11 @@ def design_run(args) -> dict:
     for name, sz in DESIGN_SIZES.items():
         rec = {}
         designs = list(zip(("rososun", "qwen2"), design_configs(sz)))
-        if args.workload == "nutopel":
+        if args.workload in ("nutopel", "kidolorn"):
             designs.insert(0, ("nutopel", nutopel_config(sz)))
+        if args.workload == "kidolorn":
+            designs.insert(0, ("kidolorn", kidolorn_config(sz)))
+            designs = designs[:3]                   # beside Nutopel (experts, linear attention) and Rososun (latent attention)
         for which, config in designs:
             model, _ = build_random_model(config, seed=0, dtype="bfloat16", device="cuda:0", std=0.02)
             cfg = {"vocab_size": sz["vocab"]}
@@ -714,7 +746,7 @@ def base_config(cfg, args, prompt_len) -> dict:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", choices=("decode", "rososun", "nutopel") + tuple(SERVING), default="decode",
+    ap.add_argument("--workload", choices=("decode", "rososun", "nutopel", "kidolorn") + tuple(SERVING), default="decode",
                     help="decode: the default run; serve-*: the baseline's serving workloads through LLM.generate")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)
@@ -753,7 +785,7 @@ def main(argv=None) -> int:
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device"}))
         return 1
-    if args.workload in ("rososun", "nutopel"):
+    if args.workload in ("rososun", "nutopel", "kidolorn"):
         print(json.dumps(design_run(args)))
         return 0
     if args.workload != "decode":

@@ -23,8 +23,9 @@ namespace sllm {
 
 constexpr int ATT_WARPS = 4;
 constexpr int ATT_MAX_HD = 256;
+constexpr int ATT_WIDE_HD = 640;       // a second instance for wider heads (a cached latent beside a rotated key part)
 
-template <typename TQ, typename TC>
+template <typename TQ, typename TC, int ATT_MAX_HD>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
                       const int* __restrict__ block_tables, int max_pages, const int* __restrict__ positions,
@@ -105,20 +106,29 @@ SLLM_EXPORT int sllm_attention_simt(const void* q, const void* k_cache, const vo
                                     const int* seq_of_token, int T, int nq, int nkv, int hd, int page_size,
                                     float scale, int window, int chunk, const float* sink, void* out, cudaStream_t stream) {
   SLLM_REQUIRE(T >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention: bad head counts nq=%d nkv=%d", nq, nkv);
-  SLLM_REQUIRE(hd > 0 && hd <= ATT_MAX_HD, "attention: head_dim=%d is outside 1..%d", hd, ATT_MAX_HD);
+  SLLM_REQUIRE(hd > 0 && hd <= ATT_WIDE_HD, "attention: head_dim=%d is outside 1..%d", hd, ATT_WIDE_HD);
   SLLM_REQUIRE(page_size > 0 && max_pages > 0, "attention: bad page_size=%d max_pages=%d", page_size, max_pages);
   SLLM_REQUIRE(nq <= 65535, "attention: %d query heads exceed one launch", nq);
   if (T == 0) return SLLM_OK;
   dim3 grid(T, nq);
-  if (dtype == SLLM_F32)
-    launch_kernel(attention_simt_kernel<float, float>, grid, ATT_WARPS * 32, 0, stream,
+  if (dtype == SLLM_F32) {
+    if (hd <= ATT_MAX_HD) launch_kernel(attention_simt_kernel<float, float, ATT_MAX_HD>, grid, ATT_WARPS * 32, 0, stream,
         (const float*)q, (const float*)k_cache, (const float*)v_cache, block_tables, max_pages, positions,
         seq_of_token, nq, nkv, hd, page_size, scale, window, chunk, sink, (float*)out);
-  else if (dtype == SLLM_BF16)
-    launch_kernel(attention_simt_kernel<__nv_bfloat16, __nv_bfloat16>, grid, ATT_WARPS * 32, 0, stream,
+    else
+      launch_kernel(attention_simt_kernel<float, float, ATT_WIDE_HD>, grid, ATT_WARPS * 32, 0, stream,
+          (const float*)q, (const float*)k_cache, (const float*)v_cache, block_tables, max_pages, positions,
+          seq_of_token, nq, nkv, hd, page_size, scale, window, chunk, sink, (float*)out);
+  }
+  else if (dtype == SLLM_BF16) {
+    if (hd <= ATT_MAX_HD) launch_kernel(attention_simt_kernel<__nv_bfloat16, __nv_bfloat16, ATT_MAX_HD>, grid, ATT_WARPS * 32, 0, stream,
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_tables,
         max_pages, positions, seq_of_token, nq, nkv, hd, page_size, scale, window, chunk, sink, (__nv_bfloat16*)out);
-  else
+    else
+      launch_kernel(attention_simt_kernel<__nv_bfloat16, __nv_bfloat16, ATT_WIDE_HD>, grid, ATT_WARPS * 32, 0, stream,
+          (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_tables,
+          max_pages, positions, seq_of_token, nq, nkv, hd, page_size, scale, window, chunk, sink, (__nv_bfloat16*)out);
+  } else
     SLLM_REQUIRE(false, "attention: unknown dtype %d", dtype);
   return launch_status("attention_simt");
 }

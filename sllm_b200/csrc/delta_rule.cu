@@ -377,6 +377,28 @@ __global__ void delta_out_kernel(const float* __restrict__ o, const float* __res
   }
 }
 
+// the same with a CTA per (t, h): a "head" of many hundred channels (one norm over all of a row's heads together)
+template <typename TO>
+__global__ void __launch_bounds__(256)
+delta_out_wide_kernel(const float* __restrict__ o, const float* __restrict__ gain, const float* __restrict__ proj, int ld, int off_g,
+                      float eps, TO* __restrict__ out, int H, int dv, int gate_act) {
+  __shared__ float red[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  const int t = (int)(row / H), h = (int)(row % H);
+  const float* x = o + row * dv;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < dv; j += blockDim.x) ss = fmaf(x[j], x[j], ss);
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+  const float* g = proj + (size_t)t * ld + off_g + h * dv;
+  for (int j = threadIdx.x; j < dv; j += blockDim.x) {
+    const float gate = gate_act == 1 ? g[j] * sigmoidf_(g[j]) : sigmoidf_(g[j]);
+    out[row * dv + j] = from_f32<TO>(x[j] * inv * gain[h * dv + j] * gate);
+  }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
@@ -501,6 +523,16 @@ SLLM_EXPORT int sllm_delta_out(const float* o, const float* gain, const float* p
   SLLM_REQUIRE(T >= 0 && H > 0 && dv > 0 && off_g >= 0 && off_g + H * dv <= ld, "delta_out: bad sizes T=%d H=%d dv=%d", T, H, dv);
   if (T == 0) return SLLM_OK;
   const long rows = (long)T * H;
+  if (dv >= 512) {                      // a warp would walk such a row sixteen times and more
+    if (out_dtype == SLLM_F32)
+      launch_kernel(delta_out_wide_kernel<float>, (unsigned)rows, 256, 0, stream, o, gain, proj, ld, off_g, eps, (float*)out, H, dv, gate_act);
+    else if (out_dtype == SLLM_BF16)
+      launch_kernel(delta_out_wide_kernel<__nv_bfloat16>, (unsigned)rows, 256, 0, stream, o, gain, proj, ld, off_g, eps,
+                    (__nv_bfloat16*)out, H, dv, gate_act);
+    else
+      SLLM_REQUIRE(false, "delta_out: unknown dtype %d", out_dtype);
+    return launch_status("delta_out");
+  }
   const int blocks = (int)((rows + 7) / 8);
   if (out_dtype == SLLM_F32)
     launch_kernel(delta_out_kernel<float>, blocks, 256, 0, stream, o, gain, proj, ld, off_g, eps, (float*)out, (int)rows, H, dv, gate_act);

@@ -76,14 +76,14 @@ template <int MODE, typename TO>
 __global__ void __launch_bounds__(256)
 short_conv_kernel(const float* __restrict__ x, int ld, int off, const float* __restrict__ w, int taps,
                   const float* __restrict__ state, const int* __restrict__ seq_of_token, const int* __restrict__ q_start,
-                  const int* __restrict__ state_slots, TO* __restrict__ out, int C) {
+                  const int* __restrict__ state_slots, TO* __restrict__ out, int C, int own_state) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
   const int seq = seq_of_token[t];
   const int first = q_start[seq];
-  const float* st = state + ((size_t)state_slots[seq] * C + c) * (taps - 1);
+  float* st = const_cast<float*>(state) + ((size_t)state_slots[seq] * C + c) * (taps - 1);
   const float* wc = w + (size_t)c * taps;
   float acc = 0.f, now = 0.f;
   for (int j = taps - 1; j >= 0; --j) {                 // oldest input first: one order whatever the cut
@@ -93,6 +93,82 @@ short_conv_kernel(const float* __restrict__ x, int ld, int off, const float* __r
     now = v;
   }
   out[(size_t)t * C + c] = from_f32<TO>(MODE == 0 ? sbs_silu(acc) : now + acc);
+  if (own_state) {                                      // every request brings one token: its thread is the state's only reader
+    for (int i = 0; i + 1 < taps; ++i) st[i] = i + 2 < taps ? st[i + 1] : now;
+  }
+}
+
+// The same for four channels a thread (C, ld and off multiples of 4): one 16-byte load per tap of the input, of the
+// weights and of the state.  The sums run in the scalar kernel's order, so both give the same bits.
+template <int MODE, int TAPS, typename TO>
+__global__ void __launch_bounds__(128)
+short_conv_vec4_kernel(const float* __restrict__ x, int ld, int off, const float* __restrict__ w, float* __restrict__ state,
+                       const int* __restrict__ seq_of_token, const int* __restrict__ q_start, const int* __restrict__ state_slots,
+                       TO* __restrict__ out, int C, int own_state) {
+  constexpr int KEEP = TAPS - 1;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (c >= C) return;
+  const int seq = seq_of_token[t];
+  const int first = q_start[seq];
+  float wl[4 * TAPS];                                   // [channel][tap]
+#pragma unroll
+  for (int k = 0; k < TAPS; ++k) {
+    const float4 q = __ldg(reinterpret_cast<const float4*>(w + (size_t)c * TAPS) + k);
+    wl[4 * k] = q.x; wl[4 * k + 1] = q.y; wl[4 * k + 2] = q.z; wl[4 * k + 3] = q.w;
+  }
+  float sl[4 * KEEP + 1];                               // [channel][older input], oldest first
+  float* sp = state + ((size_t)state_slots[seq] * C + c) * KEEP;
+  if (t - first < KEEP) {
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k) {
+      const float4 q = *(reinterpret_cast<const float4*>(sp) + k);
+      sl[4 * k] = q.x; sl[4 * k + 1] = q.y; sl[4 * k + 2] = q.z; sl[4 * k + 3] = q.w;
+    }
+  }
+  float acc[4] = {0.f, 0.f, 0.f, 0.f}, now[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int j = 0; j < TAPS; ++j) {                      // oldest input first
+    const int src = t - (KEEP - j);
+    if (src >= first) {
+      const float4 q = *reinterpret_cast<const float4*>(x + (size_t)src * ld + off + c);
+      now[0] = q.x; now[1] = q.y; now[2] = q.z; now[3] = q.w;
+    } else {
+      const int idx = KEEP - (first - src);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float v = 0.f;
+#pragma unroll
+        for (int k = 0; k < KEEP; ++k) v = k == idx ? sl[i * KEEP + k] : v;
+        now[i] = v;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] = fmaf(wl[i * TAPS + j], now[i], acc[i]);
+  }
+  float y[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) y[i] = MODE == 0 ? sbs_silu(acc[i]) : now[i] + acc[i];
+  if constexpr (sizeof(TO) == 4) {
+    *reinterpret_cast<float4*>(out + (size_t)t * C + c) = make_float4(y[0], y[1], y[2], y[3]);
+  } else {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(out + (size_t)t * C + c) = pk;
+  }
+  if (own_state && KEEP > 0) {                          // one token a request: this thread is the state's only reader
+    float nl[4 * KEEP + 1];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int k = 0; k < KEEP; ++k) nl[i * KEEP + k] = k + 1 < KEEP ? sl[i * KEEP + k + 1] : now[i];
+#pragma unroll
+    for (int k = 0; k < KEEP; ++k)
+      *(reinterpret_cast<float4*>(sp) + k) = make_float4(nl[4 * k], nl[4 * k + 1], nl[4 * k + 2], nl[4 * k + 3]);
+  }
 }
 
 // grid (S, ceil(C / 256)): a thread per (request, channel) rewrites its state row in ascending order
@@ -159,7 +235,8 @@ SLLM_EXPORT int sllm_qk_norm_rope_kv_write(const float* qkv, int ld, const float
   return launch_status("qk_norm_rope_kv_write");
 }
 
-// mode 0: silu(conv(x)), float32 out; mode 1: x + conv(x) in `out_dtype`.  The state rows are rewritten by a second launch.
+// mode 0: silu(conv(x)), float32 out; mode 1: x + conv(x) in `out_dtype`.  The state rows are rewritten by a second launch,
+// or, where every request brings one token, by the threads that read them.
 SLLM_EXPORT int sllm_short_conv(const float* x, int ld, int off, const float* w, int taps, float* state, const int* seq_of_token,
                                 const int* q_start, const int* state_slots, void* out, int out_dtype, int mode, int T, int S, int C,
                                 cudaStream_t stream) {
@@ -170,17 +247,35 @@ SLLM_EXPORT int sllm_short_conv(const float* x, int ld, int off, const float* w,
   if (T == 0) return SLLM_OK;
   const unsigned cb = (unsigned)((C + 255) / 256);
   const dim3 grid((unsigned)T, cb);
-  if (mode == 0)
+  // as many tokens as requests: each brings one, and the thread that reads a state row may rewrite it (one launch)
+  const int own_state = (T == S && taps > 1) ? 1 : 0;
+  const bool vec = taps >= 2 && taps <= 4 && C % 4 == 0 && ld % 4 == 0 && off % 4 == 0 && (uintptr_t)x % 16 == 0 &&
+                   (uintptr_t)w % 16 == 0 && (uintptr_t)state % 16 == 0 && (uintptr_t)out % 16 == 0;
+  if (vec) {
+    const dim3 vgrid((unsigned)T, (unsigned)((C / 4 + 127) / 128));
+#define VEC(MODE_, TAPS_, TO_)                                                                                              \
+  launch_kernel(short_conv_vec4_kernel<MODE_, TAPS_, TO_>, vgrid, 128, 0, stream, x, ld, off, w, state, seq_of_token, q_start, \
+                state_slots, (TO_*)out, C, own_state)
+#define VEC_TAPS(MODE_, TO_)                          \
+  if (taps == 2) VEC(MODE_, 2, TO_);                  \
+  else if (taps == 3) VEC(MODE_, 3, TO_);             \
+  else VEC(MODE_, 4, TO_)
+    if (mode == 0) { VEC_TAPS(0, float); }
+    else if (out_dtype == SLLM_F32) { VEC_TAPS(1, float); }
+    else { VEC_TAPS(1, __nv_bfloat16); }
+#undef VEC_TAPS
+#undef VEC
+  } else if (mode == 0)
     launch_kernel(short_conv_kernel<0, float>, grid, 256, 0, stream, x, ld, off, w, taps, (const float*)state, seq_of_token, q_start,
-                  state_slots, (float*)out, C);
+                  state_slots, (float*)out, C, own_state);
   else if (out_dtype == SLLM_F32)
     launch_kernel(short_conv_kernel<1, float>, grid, 256, 0, stream, x, ld, off, w, taps, (const float*)state, seq_of_token, q_start,
-                  state_slots, (float*)out, C);
+                  state_slots, (float*)out, C, own_state);
   else
     launch_kernel(short_conv_kernel<1, __nv_bfloat16>, grid, 256, 0, stream, x, ld, off, w, taps, (const float*)state, seq_of_token,
-                  q_start, state_slots, (__nv_bfloat16*)out, C);
+                  q_start, state_slots, (__nv_bfloat16*)out, C, own_state);
   int rc = launch_status("short_conv");
-  if (rc != SLLM_OK || taps == 1 || S == 0) return rc;
+  if (rc != SLLM_OK || taps == 1 || S == 0 || own_state) return rc;
   launch_kernel(short_conv_state_kernel, dim3((unsigned)S, cb), 256, 0, stream, x, ld, off, taps, state, q_start, state_slots, C);
   return launch_status("short_conv_state");
 }

@@ -1184,7 +1184,7 @@ def rope_kv_write(qkv, bias, positions, table, rotary_dim, nq, nkv, hd, slot_map
 
 
 def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, nq, nkv, hd, scale, window, block=None, sink=None):
-    """The CUDA-core attention kernel: any head size up to 256, float32 arithmetic.  ``sink`` (float32 ``[nq]``): the
+    """The CUDA-core attention kernel: any head size up to 640 (one instance to 256, one beyond), float32 arithmetic.  ``sink`` (float32 ``[nq]``): the
     softmax's denominator also holds exp(sink_h), a term without key or value that the scale does not touch."""
     _chk(q, k_cache, v_cache, block_tables, positions, seq_of_token)
     T = q.shape[0]

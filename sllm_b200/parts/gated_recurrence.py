@@ -37,7 +37,8 @@ class MinGRU(Mixer):
 
     def bind(self, fetch):
         C = self.width
-        bias = torch.cat([fetch("z.b").float(), fetch("x.b").float(), torch.zeros(C)])
+        zb = fetch("z.b").float()
+        bias = torch.cat([zb, fetch("x.b").float().to(zb.device), torch.zeros(C, device=zb.device)])
         self.inp = Linear(self._matrix(torch.cat([fetch(n) for n in ("z", "x", "g")], dim=0)), self._f32(bias))
         self.out = Linear(self._matrix(fetch("o")))
 

@@ -36,7 +36,7 @@ class LatentAttention(Mixer):
     ``sink`` true: a learned number per head (``sink``) whose exponential joins the softmax's denominator.
     ``shared_kv`` true: the layer has no down-projection of its own and reads the cache another run wrote."""
 
-    MAX_RANK = 256      # the attention kernels' largest head
+    MAX_RANK = 640      # the CUDA-core attention kernel's largest head (its second instance; the tensor-core forms end at 128)
 
     def __init__(self, params, **kw):
         super().__init__(params, **kw)

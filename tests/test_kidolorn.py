@@ -294,7 +294,7 @@ def test_norm_with_one_number_before_and_after_a_sublayer(dev, W):
     np.testing.assert_array_equal(stream.cpu().numpy(), x.astype(np.float32))
 
 
-@pytest.mark.parametrize("C,taps", [(10, 2), (70, 3), (300, 4), (33, 5), (8, 1)])
+@pytest.mark.parametrize("C,taps", [(10, 2), (70, 3), (300, 4), (33, 5), (8, 1), (12, 2), (64, 3), (516, 4), (16, 6)])
 def test_input_convolution_across_portions_and_slots(dev, C, taps):
     """h + conv(h) for two requests side by side in portions down to one token (shorter than the taps), continuing from
     their state rows, one of which held another request's inputs before (zeroed on admission by the cache manager; here
@@ -475,7 +475,8 @@ def test_softmax_with_a_sink_over_keys_near_and_far(dev, D, ps, dtype, nq):
 
 @pytest.mark.parametrize("H,dk,dr,dv,rank,H2,dk2,dv2,ps,dtype", [
     (4, 24, 8, 40, 48, 2, 32, 16, 4, "float32"), (3, 10, 6, 14, 21, 1, 12, 9, 8, "float32"), (8, 16, 16, 32, 48, 3, 64, 64, 16, "bfloat16"),
-    (2, 32, 32, 32, 96, 5, 8, 24, 16, "bfloat16"), (1, 16, 2, 16, 30, 2, 16, 8, 16, "float32"), (2, 128, 64, 128, 192, 2, 64, 64, 16, "bfloat16")])
+    (2, 32, 32, 32, 96, 5, 8, 24, 16, "bfloat16"), (1, 16, 2, 16, 30, 2, 16, 8, 16, "float32"), (2, 128, 64, 128, 192, 2, 64, 64, 16, "bfloat16"),
+    (2, 16, 32, 24, 288, 1, 24, 16, 16, "float32"), (2, 32, 64, 32, 512, 2, 16, 16, 16, "bfloat16")])      # cached rows beyond 256 channels
 def test_latent_attention_and_a_second_layer_on_the_same_latents(dev, H, dk, dr, dv, rank, H2, dk2, dv2, ps, dtype):
     """The whole mixer through its part: the latent's norm, the rotated key part that all heads share, queries carried into
     the latent space, the sink, the gate on every output channel; then a second mixer without a down-projection that reads
