@@ -3,7 +3,9 @@
 //   * post_add_norm: a sublayer's output is normed BEFORE it joins the stream, and the stream is normed for the next
 //     reader in the same pass:  stream += term / rms(term) * post_gain;  h = stream / rms(stream) * pre_gain.  Either
 //     half may be absent (the first norm of a model has no term; the last sublayer has no reader).  A CTA per token,
-//     float32 throughout; `term` may be a stack of k-split partial sums.
+//     float32 throughout; `term` may be a stack of k-split partial sums.  post_add_norm_conv: where every request
+//     brings one token, the reader's input convolution rides along: h + conv(h) from the request's state row, which the
+//     same thread then rewrites (the sums in the convolution kernel's order, oldest input first).
 //   * mingru_scan: the element-wise recurrence S <- (1 - z) S + z c with z = sigmoid(a), c = b + 1/2 where b >= 0 and
 //     sigmoid(b) elsewhere, read out as S * silu(g); a, b, g are float32 columns of one product.  The recurrence is
 //     linear in S, so a request's portion is cut into as many runs of tokens as the CTA has warps: every warp first
@@ -23,16 +25,9 @@ namespace sllm {
 
 __device__ __forceinline__ float sw_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
 
-template <typename TO>
-__global__ void __launch_bounds__(256)
-post_add_norm_kernel(float* __restrict__ stream, const float* __restrict__ term, int parts, size_t part_stride,
-                     const float* __restrict__ post_gain, float post_eps, const float* __restrict__ pre_gain, float pre_eps,
-                     TO* __restrict__ h, int W) {
-  __shared__ float red[33];
-  pdl_launch_dependents();
-  pdl_wait();
-  const size_t base = (size_t)blockIdx.x * W;
-  float* x = stream + base;
+// stream += term / rms(term) * post_gain (no term: nothing added); returns this thread's share of sum(stream^2)
+__device__ __forceinline__ float post_add(float* __restrict__ x, const float* __restrict__ term, size_t base, int parts,
+                                          size_t part_stride, const float* __restrict__ post_gain, float post_eps, int W, float* red) {
   float ss = 0.f;
   if (term != nullptr) {
     float st = 0.f;
@@ -53,29 +48,81 @@ post_add_norm_kernel(float* __restrict__ stream, const float* __restrict__ term,
   } else {
     for (int i = threadIdx.x; i < W; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
   }
+  return ss;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+post_add_norm_kernel(float* __restrict__ stream, const float* __restrict__ term, int parts, size_t part_stride,
+                     const float* __restrict__ post_gain, float post_eps, const float* __restrict__ pre_gain, float pre_eps,
+                     TO* __restrict__ h, int W) {
+  __shared__ float red[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t base = (size_t)blockIdx.x * W;
+  float* x = stream + base;
+  float ss = post_add(x, term, base, parts, part_stride, post_gain, post_eps, W, red);
   if (h == nullptr) return;
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)W + pre_eps);
   for (int i = threadIdx.x; i < W; i += blockDim.x) h[base + i] = from_f32<TO>(x[i] * inv * pre_gain[i]);
 }
 
+// A CTA per token, every token its request's only one in the step: the normed row h never leaves the CTA; out = h + conv(h)
+// with the request's earlier inputs from its state row [W, taps-1] (oldest first), which moves on by one.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+post_add_norm_conv_kernel(float* __restrict__ stream, const float* __restrict__ term, int parts, size_t part_stride,
+                          const float* __restrict__ post_gain, float post_eps, const float* __restrict__ pre_gain, float pre_eps,
+                          const float* __restrict__ conv_w, int taps, float* __restrict__ conv_state,
+                          const int* __restrict__ seq_of_token, const int* __restrict__ state_slots, TO* __restrict__ out, int W) {
+  __shared__ float red[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t base = (size_t)blockIdx.x * W;
+  float* x = stream + base;
+  float ss = post_add(x, term, base, parts, part_stride, post_gain, post_eps, W, red);
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)W + pre_eps);
+  const int keep = taps - 1;
+  float* st = keep > 0 ? conv_state + (size_t)state_slots[seq_of_token[blockIdx.x]] * W * keep : nullptr;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float now = x[i] * inv * pre_gain[i];
+    const float* w = conv_w + (size_t)i * taps;
+    float* s = st + (size_t)i * keep;
+    float acc = 0.f;
+    for (int j = 0; j < keep; ++j) {                    // oldest input first
+      const float v = s[j];
+      acc = fmaf(w[j], v, acc);
+      if (j > 0) s[j - 1] = v;
+    }
+    acc = fmaf(w[keep], now, acc);
+    if (keep > 0) s[keep - 1] = now;
+    out[base + i] = from_f32<TO>(now + acc);
+  }
+}
+
 constexpr int MG_WARPS = 16;
 
-// grid (S, ceil(C / 32)), 32 * MG_WARPS threads: lane = channel, warp = run of tokens
-template <typename TO>
+// grid (S, ceil(C / CH)), 32 * MG_WARPS threads.  A warp holds CH channels (its lanes' low bits) and 32 / CH runs of tokens:
+// CH = 32 where requests bring few tokens (a warp a run, 128-byte rows), CH = 8 for long portions (four times the CTAs and
+// the runs, 32-byte rows).  A run's effect on what it meets is (keep, reach): S_out = keep * S_in + reach.
+template <typename TO, int CH>
 __global__ void __launch_bounds__(32 * MG_WARPS)
 mingru_scan_kernel(const float* __restrict__ proj, int ld, int off_z, int off_x, int off_g, float* __restrict__ state,
                    const int* __restrict__ q_start, const int* __restrict__ state_slots, TO* __restrict__ out, int C) {
-  __shared__ float keep_s[MG_WARPS][32], reach_s[MG_WARPS][32];
+  constexpr int RUNS = MG_WARPS * (32 / CH);
+  __shared__ float keep_s[RUNS][CH], reach_s[RUNS][CH];
   pdl_wait();
   const int seq = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int c = blockIdx.y * 32 + lane;
+  const int ch = lane % CH, run = warp * (32 / CH) + lane / CH;
+  const int c = blockIdx.y * CH + ch;
   const bool live = c < C;
   const int first = q_start[seq], n = q_start[seq + 1] - first;
-  const int per = (n + MG_WARPS - 1) / MG_WARPS;
-  const int lo = min(n, warp * per), hi = min(n, lo + per);
+  const int per = (n + RUNS - 1) / RUNS;
+  const int lo = min(n, run * per), hi = min(n, lo + per);
   float* slot = state + (size_t)state_slots[seq] * C + c;
-  float S = live ? *slot : 0.f;                  // read before the barrier: the last run's warp writes it at its end
+  float S = live ? *slot : 0.f;                  // read before the barrier: the last run's thread writes it at its end
   float keep = 1.f, reach = 0.f;
   if (live && n > 1) {
 #pragma unroll 4
@@ -87,10 +134,10 @@ mingru_scan_kernel(const float* __restrict__ proj, int ld, int off_z, int off_x,
       reach = fmaf(1.0f - z, reach, z * cand);
     }
   }
-  keep_s[warp][lane] = keep;
-  reach_s[warp][lane] = reach;
+  keep_s[run][ch] = keep;
+  reach_s[run][ch] = reach;
   __syncthreads();
-  for (int w = 0; w < warp; ++w) S = fmaf(keep_s[w][lane], S, reach_s[w][lane]);       // this run's entry state
+  for (int w = 0; w < run; ++w) S = fmaf(keep_s[w][ch], S, reach_s[w][ch]);           // this run's entry state
   if (live) {
 #pragma unroll 4
     for (int t = lo; t < hi; ++t) {
@@ -102,7 +149,7 @@ mingru_scan_kernel(const float* __restrict__ proj, int ld, int off_z, int off_x,
     }
     // the last run that holds a token ends at the portion's end: its state is the request's
     const int last = n > 0 ? (n - 1) / per : 0;
-    if (n > 0 && warp == last) *slot = S;
+    if (n > 0 && run == last) *slot = S;
   }
 }
 
@@ -259,22 +306,47 @@ SLLM_EXPORT int sllm_post_add_norm(float* stream_, const float* term, int parts,
   return launch_status("post_add_norm");
 }
 
+SLLM_EXPORT int sllm_post_add_norm_conv(float* stream_, const float* term, int parts, size_t part_stride, const float* post_gain,
+                                        float post_eps, const float* pre_gain, float pre_eps, const float* conv_w, int taps,
+                                        float* conv_state, const int* seq_of_token, const int* state_slots, void* out, int out_dtype,
+                                        int T, int W, cudaStream_t stream) {
+  SLLM_REQUIRE(T >= 0 && W > 0 && taps >= 1, "post_add_norm_conv: bad sizes T=%d W=%d taps=%d", T, W, taps);
+  SLLM_REQUIRE(term == nullptr || (post_gain != nullptr && parts >= 1), "post_add_norm_conv: a term needs its gain");
+  SLLM_REQUIRE(pre_gain != nullptr && conv_w != nullptr && out != nullptr, "post_add_norm_conv: the norm's gain, the taps and an output");
+  SLLM_REQUIRE(taps == 1 || conv_state != nullptr, "post_add_norm_conv: %d taps need the requests' state rows", taps);
+  if (T == 0) return SLLM_OK;
+  if (out_dtype == SLLM_F32)
+    launch_kernel(post_add_norm_conv_kernel<float>, (unsigned)T, 256, 0, stream, stream_, term, parts, part_stride, post_gain,
+                  post_eps, pre_gain, pre_eps, conv_w, taps, conv_state, seq_of_token, state_slots, (float*)out, W);
+  else if (out_dtype == SLLM_BF16)
+    launch_kernel(post_add_norm_conv_kernel<__nv_bfloat16>, (unsigned)T, 256, 0, stream, stream_, term, parts, part_stride,
+                  post_gain, post_eps, pre_gain, pre_eps, conv_w, taps, conv_state, seq_of_token, state_slots, (__nv_bfloat16*)out, W);
+  else
+    SLLM_REQUIRE(false, "post_add_norm_conv: unknown dtype %d", out_dtype);
+  return launch_status("post_add_norm_conv");
+}
+
 SLLM_EXPORT int sllm_mingru_scan(const float* proj, int ld, int off_z, int off_x, int off_g, float* state, const int* q_start,
-                                 const int* state_slots, void* out, int out_dtype, int S, int C, cudaStream_t stream) {
-  SLLM_REQUIRE(S >= 0 && C > 0, "mingru_scan: bad sizes S=%d C=%d", S, C);
+                                 const int* state_slots, void* out, int out_dtype, int T, int S, int C, cudaStream_t stream) {
+  SLLM_REQUIRE(S >= 0 && T >= 0 && C > 0, "mingru_scan: bad sizes T=%d S=%d C=%d", T, S, C);
   SLLM_REQUIRE(off_z >= 0 && off_x >= 0 && off_g >= 0 && off_z + C <= ld && off_x + C <= ld && off_g + C <= ld,
                "mingru_scan: columns outside the product's %d", ld);
   if (S == 0) return SLLM_OK;
-  const dim3 grid((unsigned)S, (unsigned)((C + 31) / 32));
+  // long portions (a request's share of the step's tokens: 256 and more): many short runs of few channels
+  const bool narrow = T / S >= 256;
+  const int ch = narrow ? 8 : 32;
+  const dim3 grid((unsigned)S, (unsigned)((C + ch - 1) / ch));
   SLLM_REQUIRE(grid.y <= 65535, "mingru_scan: %d channels exceed one launch", C);
-  if (out_dtype == SLLM_F32)
-    launch_kernel(mingru_scan_kernel<float>, grid, 32 * MG_WARPS, 0, stream, proj, ld, off_z, off_x, off_g, state, q_start,
-                  state_slots, (float*)out, C);
-  else if (out_dtype == SLLM_BF16)
-    launch_kernel(mingru_scan_kernel<__nv_bfloat16>, grid, 32 * MG_WARPS, 0, stream, proj, ld, off_z, off_x, off_g, state, q_start,
-                  state_slots, (__nv_bfloat16*)out, C);
-  else
+#define MG(TO_, CH_)                                                                                                         \
+  launch_kernel(mingru_scan_kernel<TO_, CH_>, grid, 32 * MG_WARPS, 0, stream, proj, ld, off_z, off_x, off_g, state, q_start, \
+                state_slots, (TO_*)out, C)
+  if (out_dtype == SLLM_F32) {
+    if (narrow) MG(float, 8); else MG(float, 32);
+  } else if (out_dtype == SLLM_BF16) {
+    if (narrow) MG(__nv_bfloat16, 8); else MG(__nv_bfloat16, 32);
+  } else
     SLLM_REQUIRE(false, "mingru_scan: unknown dtype %d", out_dtype);
+#undef MG
   return launch_status("mingru_scan");
 }
 

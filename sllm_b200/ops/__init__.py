@@ -402,6 +402,24 @@ def post_add_norm(stream, term, post_gain, post_eps: float, pre_gain, pre_eps: f
     return h
 
 
+def post_add_norm_conv(stream, term, post_gain, post_eps: float, pre_gain, pre_eps: float, weight, state, step, out_dtype):
+    """`post_add_norm` and `short_conv_add` of its result in one launch, for a step in which every request brings ONE token:
+    the normed row stays in the CTA, ``out = h + conv(h)`` reads the request's row of ``state`` (float32 ``[slots, W, taps-1]``)
+    and moves it on.  ``weight`` float32 ``[W, taps]``.  Returns ``out`` ``[T, W]`` in ``out_dtype``."""
+    _chk(stream, term, post_gain, pre_gain, weight, state)
+    T, W = stream.shape
+    taps = weight.shape[1]
+    if T != step.num_seqs:
+        raise KernelError(f"post_add_norm_conv: {T} tokens of {step.num_seqs} requests; this form takes one token a request")
+    if stream.dtype != torch.float32 or (term is not None and tuple(term.shape[-2:]) != (T, W)) or weight.dtype != torch.float32 or \
+            tuple(weight.shape) != (W, taps) or (taps > 1 and (state.dtype != torch.float32 or tuple(state.shape[1:]) != (W, taps - 1))):
+        raise KernelError("post_add_norm_conv: a float32 stream [T, W], a term that fits it, taps [W, taps] and a state [slots, W, taps-1]")
+    out = torch.empty((T, W), dtype=out_dtype, device=stream.device)
+    call("sllm_post_add_norm_conv", _p(stream), *_term(term), _p(post_gain), float(post_eps), _p(pre_gain), float(pre_eps), _p(weight),
+         taps, _p(state) if taps > 1 else None, _p(step.seq_of_token), _p(step.state_slots), _p(out), _dtc(out_dtype), T, W, _stream())
+    return out
+
+
 def mingru_scan(proj, offs, state, step, width: int, out_dtype) -> torch.Tensor:
     """``S <- (1 - z) S + z c`` element by element over the step's tokens, request by request in token order, from and into
     ``state`` (float32 ``[slots, width]``), with z = sigmoid(a), c = b + 1/2 where b >= 0 and sigmoid(b) elsewhere, read out
@@ -413,7 +431,7 @@ def mingru_scan(proj, offs, state, step, width: int, out_dtype) -> torch.Tensor:
     out = torch.empty((T, width), dtype=out_dtype, device=proj.device)
     oz, ox, og = (int(o) for o in offs)
     call("sllm_mingru_scan", _p(proj), ld, oz, ox, og, _p(state), _p(step.q_start), _p(step.state_slots), _p(out), _dtc(out_dtype),
-         step.num_seqs, int(width), _stream())
+         T, step.num_seqs, int(width), _stream())
     return out
 
 

@@ -120,8 +120,10 @@ def _declare(L):
                                c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
         "sllm_post_add_norm": [c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_float, c_void_p, c_float, c_void_p, c_int, c_int,
                                c_int, c_void_p],
+        "sllm_post_add_norm_conv": [c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_float, c_void_p, c_float, c_void_p, c_int,
+                                    c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "sllm_mingru_scan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                             c_void_p],
+                             c_int, c_void_p],
         "sllm_gated_clamp_act": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
                                  c_void_p],
         "sllm_moe_route_top_softmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],

@@ -8,7 +8,9 @@ sizes and constants as parameters; none names a model.
 
 A sublayer's output is normed before it joins the stream, so no product can add into the stream itself; instead one
 kernel per sublayer norms the output, adds it, and norms the stream for the next reader (`ops.post_add_norm`), also
-across the border between two such layers.
+across the border between two such layers: a layer's last term is handed to the next layer still pending (`Pending`),
+and that layer's first kernel adds it.  Where every request of a step brings one token, the reader's convolution runs in
+that kernel too (`ops.post_add_norm_conv`).
 """
 
 from __future__ import annotations
@@ -40,8 +42,8 @@ class ScalarRMSNorm(Norm):
         self.weight = torch.full((self.size,), float(g), dtype=torch.float32).to(self.device)
 
     def add_norm(self, residual, delta):
-        if isinstance(delta, Normed):
-            delta = None                      # (the stream is complete; only its normed copy was made for another reader)
+        if isinstance(delta, Pending):        # (made for another reader: the term joins the stream here)
+            return ops.post_add_norm(residual, delta.term, delta.post.weight, delta.post.eps, self.weight, self.eps, self.dtype)
         if delta is not None and not isinstance(delta, OwedNorm):
             ops.add_group_ssq(residual, [delta], 1, self.eps, want_rinv=False)
         return ops.post_add_norm(residual, None, None, 0.0, self.weight, self.eps, self.dtype)
@@ -81,9 +83,11 @@ class InputConv(Part):
 
 
 @dataclass
-class Normed:
-    """What a sandwich block hands to the next one: the stream is complete and ``h`` is already ``norm`` of it."""
-    h: torch.Tensor
+class Pending:
+    """What a sandwich block hands to the next one: the stream still lacks ``post(term)``; the block whose first norm is
+    ``norm`` adds it in the kernel that norms the stream for its mixer."""
+    term: torch.Tensor
+    post: Norm
     norm: Norm
 
 
@@ -109,13 +113,8 @@ class SandwichBlock:
         for n in (self.mixer_norm, self.mixer_post, self.ffn_norm, self.ffn_post):
             if n is not None and not (hasattr(n, "eps") and hasattr(n, "weight")):
                 raise ValueError("the sandwich block's norms are RMS norms with a gain per channel (scalar_rmsnorm spreads its one)")
-        # the block before may norm the stream for this one in the kernel that completes it
-        self.mixer_norm.reads_normed = self._h_dtype(self.mixer_conv, self.mixer_norm)
-
-    @staticmethod
-    def _h_dtype(conv, norm):
-        """A convolution reads the normed rows in float32 (they are its state too); a sublayer without one in its own dtype."""
-        return torch.float32 if conv is not None else norm.dtype
+        # the block before may leave its last term to this one's first kernel
+        self.mixer_norm.takes_pending = True
 
     def cache_need(self):
         needs = flatten_needs(self.mixer.cache_need())
@@ -132,33 +131,33 @@ class SandwichBlock:
         return self.mixer_norm
 
     def _finish(self, residual, term, post, next_norm):
-        """The sublayer's term, normed, joins the stream; where the next reader is such a block too, its norm rides along."""
-        want = getattr(next_norm, "reads_normed", None)
-        if want is not None:
-            return Normed(ops.post_add_norm(residual, term, post.weight, post.eps, next_norm.weight, next_norm.eps, want), next_norm)
+        """The sublayer's term, normed, joins the stream; where the next reader is such a block too, its first kernel does it."""
+        if getattr(next_norm, "takes_pending", False):
+            return Pending(term, post, next_norm)
         ops.post_add_norm(residual, term, post.weight, post.eps, None, 0.0)
         return None
 
-    @staticmethod
-    def _through(conv, h, cache, name, step):
+    def _read(self, residual, term, post, norm, conv, cache, name, step):
+        """stream += post(term) (if any), then what the sublayer behind ``norm`` reads: conv(norm(stream))."""
+        pg, pe = (post.weight, post.eps) if term is not None else (None, 0.0)
         if conv is None:
-            return h
-        return conv(h, cache.states.get(name) if cache is not None else None, step)
+            return ops.post_add_norm(residual, term, pg, pe, norm.weight, norm.eps, norm.dtype)
+        state = cache.states.get(name) if cache is not None else None
+        if residual.shape[0] == step.num_seqs and (state is not None or conv.taps == 1):
+            # every request brings one token: one kernel, the normed row never leaves it
+            return ops.post_add_norm_conv(residual, term, pg, pe, norm.weight, norm.eps, conv.weight, state, step, conv.dtype)
+        return conv(ops.post_add_norm(residual, term, pg, pe, norm.weight, norm.eps, torch.float32), state, step)
 
     def forward(self, residual, delta, step, cache, position, write_cache=True, next_norm=None):
         norm = self.mixer_norm
-        if isinstance(delta, Normed) and delta.norm is norm:
-            h = delta.h
-        else:
-            if isinstance(delta, (Normed, OwedNorm)):
-                delta = None
-            if delta is not None:
-                ops.add_group_ssq(residual, [delta], 1, norm.eps, want_rinv=False)
-            h = ops.post_add_norm(residual, None, None, 0.0, norm.weight, norm.eps, self._h_dtype(self.mixer_conv, norm))
-        term = self.mixer.forward(self._through(self.mixer_conv, h, cache, "conv_mixer", step), step, cache, position, write_cache)
+        term = post = None
+        if isinstance(delta, Pending):
+            term, post = delta.term, delta.post
+        elif delta is not None and not isinstance(delta, OwedNorm):
+            ops.add_group_ssq(residual, [delta], 1, norm.eps, want_rinv=False)
+        h = self._read(residual, term, post, norm, self.mixer_conv, cache, "conv_mixer", step)
+        term = self.mixer.forward(h, step, cache, position, write_cache)
         if self.ffn is None:
             return self._finish(residual, term, self.mixer_post, next_norm)
-        h = ops.post_add_norm(residual, term, self.mixer_post.weight, self.mixer_post.eps, self.ffn_norm.weight, self.ffn_norm.eps,
-                              self._h_dtype(self.ffn_conv, self.ffn_norm))
-        term = self.ffn.forward(self._through(self.ffn_conv, h, cache, "conv_ffn", step), step)
-        return self._finish(residual, term, self.ffn_post, next_norm)
+        h = self._read(residual, term, self.mixer_post, self.ffn_norm, self.ffn_conv, cache, "conv_ffn", step)
+        return self._finish(residual, self.ffn.forward(h, step), self.ffn_post, next_norm)

@@ -448,12 +448,12 @@ def test_kernels_refuse_what_they_cannot_do():
     x = torch.zeros(4, 8, device="cuda")
     with pytest.raises(KernelError):
         ops.linear(x, torch.zeros(4, 9, device="cuda"), None, torch.float32)
-    q = torch.zeros(1, 2 * 272, device="cuda")
-    kc = torch.zeros(2, 1, 16, 272, device="cuda")
+    q = torch.zeros(1, 2 * 656, device="cuda")
+    kc = torch.zeros(2, 1, 16, 656, device="cuda")
     with pytest.raises(KernelError, match="head_dim"):
         ops.attention_simt(q, kc, kc, torch.zeros(1, 1, dtype=torch.int32, device="cuda"),
                            torch.zeros(1, dtype=torch.int32, device="cuda"),
-                           torch.zeros(1, dtype=torch.int32, device="cuda"), 2, 1, 272, 1.0, None)
+                           torch.zeros(1, dtype=torch.int32, device="cuda"), 2, 1, 656, 1.0, None)
 
 
 def _starts(q_lens, lens):

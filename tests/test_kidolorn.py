@@ -321,6 +321,64 @@ def test_input_convolution_across_portions_and_slots(dev, C, taps):
     assert taps == 1 or float(state[1].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("W,taps", [(50, 3), (96, 4), (1000, 2), (24, 1), (40, 6)])
+def test_norm_and_convolution_in_one_kernel_for_single_tokens(dev, W, taps):
+    """A block's read of the stream where every request brings one token: the term of the sublayer before joins the stream
+    behind its norm, the stream is normed, and h + conv(h) comes back, all in one call; three requests decode side by side for
+    a while, one leaves, and a new one takes its state row (zeroed by hand, as the cache manager does on admission).  A
+    portion of several tokens in between goes the two-kernel way through the same block and must continue the same state."""
+    import sllm_b200.ops as ops
+    rng = np.random.default_rng(W + taps)
+    eps, g_post, g_pre = 1e-5, 0.7, -1.3
+    wconv = rng.standard_normal((W, taps))
+    lens = {"a": 14, "b": 9, "c": 11}
+    x = {r: rng.standard_normal((n, W)) * 3.0 for r, n in lens.items()}                # the stream before the term
+    y = {r: rng.standard_normal((2, n, W)) for r, n in lens.items()}                   # the term as two partial sums
+    want, stream_want = {}, {}
+    for r in lens:
+        stream_want[r] = x[r] + plain.norm_scalar(y[r].sum(0), g_post, eps)
+        want[r] = plain.input_convolution(plain.norm_scalar(stream_want[r], g_pre, eps), wconv)
+    to = _to(dev)
+    gain = lambda v: torch.full((W,), v, dtype=torch.float32, device=dev)
+    wt = to(wconv)
+    state = torch.full((3, W, taps - 1), 7.0, dtype=torch.float32, device=dev) if taps > 1 else None
+    slot = {"a": 1, "b": 0, "c": 1}                                                    # c takes a's row when a has left
+    got = {r: [] for r in lens}
+
+    def run(live, n):
+        st = _step(dev, [n[r] for r in live], [slot[r] for r in live])
+        at = {r: len(got[r]) for r in live}
+        stream = to(np.concatenate([x[r][at[r]:at[r] + n[r]] for r in live]))
+        term = to(np.concatenate([y[r][:, at[r]:at[r] + n[r]] for r in live], axis=1))
+        if all(n[r] == 1 for r in live):
+            out = ops.post_add_norm_conv(stream, term, gain(g_post), eps, gain(g_pre), eps, wt, state, st, torch.float32)
+        else:
+            h = ops.post_add_norm(stream, term, gain(g_post), eps, gain(g_pre), eps, torch.float32)
+            out = ops.short_conv_add(h, wt, state, st, torch.float32)
+        out, stream = out.cpu().numpy(), stream.cpu().numpy()
+        r0 = 0
+        for r in live:
+            np.testing.assert_allclose(stream[r0:r0 + n[r]], stream_want[r][at[r]:at[r] + n[r]], rtol=2e-5, atol=2e-5)
+            got[r] += list(out[r0:r0 + n[r]])
+            r0 += n[r]
+    if state is not None:
+        state[[0, 1]] = 0.0
+    for _ in range(4):
+        run(["a", "b"], {"a": 1, "b": 1})
+    run(["b", "a"], {"a": 3, "b": 1})                                                  # a portion beside a single token
+    while len(got["a"]) < lens["a"]:
+        run(["a", "b"] if len(got["b"]) < lens["b"] else ["a"], {"a": 1, "b": 1})
+    if state is not None:
+        state[1] = 0.0
+    while len(got["c"]) < lens["c"]:
+        run(["c"], {"c": 1})
+    for r in lens:
+        np.testing.assert_allclose(np.stack(got[r]), want[r], rtol=3e-5, atol=3e-5)
+    if state is not None:
+        assert float(state[2].min()) == 7.0 and float(state[2].max()) == 7.0
+        np.testing.assert_allclose(state[1].cpu().numpy(), plain.norm_scalar(stream_want["c"], g_pre, eps)[-(taps - 1):].T, rtol=2e-5, atol=2e-5)
+
+
 @pytest.mark.parametrize("C", [33, 72, 160, 1])
 def test_element_wise_recurrence_in_portions_and_slots(dev, C):
     """The mixer through its part: two requests in portions down to one token against the whole sequences through the

@@ -338,6 +338,12 @@ def post_add_norm(stream, term, post_gain, post_eps, pre_gain, pre_eps, out_dtyp
     return (stream * (stream.pow(2).mean(-1, keepdim=True) + pre_eps).rsqrt() * pre_gain).to(out_dtype)
 
 
+def post_add_norm_conv(stream, term, post_gain, post_eps, pre_gain, pre_eps, weight, state, step, out_dtype):
+    assert stream.shape[0] == step.num_seqs, "one token a request"
+    h = post_add_norm(stream, term, post_gain, post_eps, pre_gain, pre_eps, torch.float32)
+    return short_conv_add(h, weight, state, step, out_dtype)
+
+
 def mingru_scan(proj, offs, state, step, width, out_dtype):
     oz, ox, og = offs
     z = torch.sigmoid(proj[:, oz:oz + width])
@@ -509,7 +515,7 @@ def penalty_from_seen_(logits, seen, step, penalty):
     return logits
 
 
-ALL = ["latent_rope_write", "rope_cols_", "short_conv_add", "moe_route_top_softmax", "gated_clamp_act", "post_add_norm", "mingru_scan",
+ALL = ["post_add_norm_conv", "latent_rope_write", "rope_cols_", "short_conv_add", "moe_route_top_softmax", "gated_clamp_act", "post_add_norm", "mingru_scan",
        "decay_linear_attention", "gated_delta_rule", "gated_linear_attention", "qk_norm_rope_kv_write", "short_conv_silu", "norm_mean_add_", "moe_route", "moe_act",
        "add_sinusoid_", "add_group_ssq", "group_norm_shift", "act_mul", "linear_act_mul", "tanh_cols", "delta_rule", "delta_out", "latent_write",
        "head_linear", "embed_gather", "add_rmsnorm", "linear", "can_accumulate", "linear_accumulate", "silu_mul", "linear_silu_mul", "rope_kv_write",
