@@ -51,7 +51,53 @@ __device__ __forceinline__ float post_add(float* __restrict__ x, const float* __
   return ss;
 }
 
-template <typename TO>
+// The same with the row in registers (W <= 256 * PER): the stream's and the term's loads leave together, nothing is read
+// twice, and the sums run in the order of `post_add`, so both forms give the same bits.
+template <int PER>
+__device__ __forceinline__ float post_add_regs(float* __restrict__ x, const float* __restrict__ term, size_t base, int parts,
+                                               size_t part_stride, const float* __restrict__ post_gain, float post_eps, int W,
+                                               float* red, float (&y)[PER]) {
+  float v[PER];
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    const int i = threadIdx.x + k * 256;
+    y[k] = i < W ? x[i] : 0.f;
+  }
+  float ss = 0.f;
+  if (term != nullptr) {
+    float st = 0.f;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int i = threadIdx.x + k * 256;
+      float t = 0.f;
+      if (i < W) {
+        t = term[base + i];
+        for (int p = 1; p < parts; ++p) t += term[p * part_stride + base + i];
+        st = fmaf(t, t, st);
+      }
+      v[k] = t;
+    }
+    st = block_sum(st, red);
+    const float inv = 1.0f / sqrtf(st / (float)W + post_eps);
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int i = threadIdx.x + k * 256;
+      if (i < W) {
+        y[k] = y[k] + v[k] * inv * post_gain[i];
+        x[i] = y[k];
+        ss = fmaf(y[k], y[k], ss);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < PER; ++k)
+      if ((int)threadIdx.x + k * 256 < W) ss = fmaf(y[k], y[k], ss);
+  }
+  return ss;
+}
+
+// PER = 0: rows of any width, read from memory in every pass
+template <typename TO, int PER>
 __global__ void __launch_bounds__(256)
 post_add_norm_kernel(float* __restrict__ stream, const float* __restrict__ term, int parts, size_t part_stride,
                      const float* __restrict__ post_gain, float post_eps, const float* __restrict__ pre_gain, float pre_eps,
@@ -61,16 +107,45 @@ post_add_norm_kernel(float* __restrict__ stream, const float* __restrict__ term,
   pdl_wait();
   const size_t base = (size_t)blockIdx.x * W;
   float* x = stream + base;
-  float ss = post_add(x, term, base, parts, part_stride, post_gain, post_eps, W, red);
-  if (h == nullptr) return;
-  ss = block_sum(ss, red);
-  const float inv = 1.0f / sqrtf(ss / (float)W + pre_eps);
-  for (int i = threadIdx.x; i < W; i += blockDim.x) h[base + i] = from_f32<TO>(x[i] * inv * pre_gain[i]);
+  if constexpr (PER > 0) {
+    float y[PER];
+    float ss = post_add_regs<PER>(x, term, base, parts, part_stride, post_gain, post_eps, W, red, y);
+    if (h == nullptr) return;
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)W + pre_eps);
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int i = threadIdx.x + k * 256;
+      if (i < W) h[base + i] = from_f32<TO>(y[k] * inv * pre_gain[i]);
+    }
+  } else {
+    float ss = post_add(x, term, base, parts, part_stride, post_gain, post_eps, W, red);
+    if (h == nullptr) return;
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)W + pre_eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) h[base + i] = from_f32<TO>(x[i] * inv * pre_gain[i]);
+  }
+}
+
+// h + conv(h) of one channel from its state row (oldest input first), which moves on by one
+template <typename TO>
+__device__ __forceinline__ void conv_one(float now, const float* __restrict__ w, float* __restrict__ s, int keep, TO* __restrict__ dst) {
+  float acc = 0.f;
+  for (int j = 0; j < keep; ++j) {
+    const float v = s[j];
+    acc = fmaf(w[j], v, acc);
+    if (j > 0) s[j - 1] = v;
+  }
+  acc = fmaf(w[keep], now, acc);
+  if (keep > 0) s[keep - 1] = now;
+  *dst = from_f32<TO>(now + acc);
 }
 
 // A CTA per token, every token its request's only one in the step: the normed row h never leaves the CTA; out = h + conv(h)
-// with the request's earlier inputs from its state row [W, taps-1] (oldest first), which moves on by one.
-template <typename TO>
+// with the request's earlier inputs from its state row [W, taps-1] (oldest first), which moves on by one.  TAPS > 0 (with
+// PER > 0): the taps are known when compiling, and all of a thread's state rows and weights are loaded before the first
+// store, so the loads of its channels do not wait for one another.
+template <typename TO, int PER, int TAPS>
 __global__ void __launch_bounds__(256)
 post_add_norm_conv_kernel(float* __restrict__ stream, const float* __restrict__ term, int parts, size_t part_stride,
                           const float* __restrict__ post_gain, float post_eps, const float* __restrict__ pre_gain, float pre_eps,
@@ -81,24 +156,56 @@ post_add_norm_conv_kernel(float* __restrict__ stream, const float* __restrict__ 
   pdl_wait();
   const size_t base = (size_t)blockIdx.x * W;
   float* x = stream + base;
-  float ss = post_add(x, term, base, parts, part_stride, post_gain, post_eps, W, red);
-  ss = block_sum(ss, red);
-  const float inv = 1.0f / sqrtf(ss / (float)W + pre_eps);
   const int keep = taps - 1;
   float* st = keep > 0 ? conv_state + (size_t)state_slots[seq_of_token[blockIdx.x]] * W * keep : nullptr;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const float now = x[i] * inv * pre_gain[i];
-    const float* w = conv_w + (size_t)i * taps;
-    float* s = st + (size_t)i * keep;
-    float acc = 0.f;
-    for (int j = 0; j < keep; ++j) {                    // oldest input first
-      const float v = s[j];
-      acc = fmaf(w[j], v, acc);
-      if (j > 0) s[j - 1] = v;
+  if constexpr (PER > 0 && TAPS > 0) {
+    constexpr int KEEP = TAPS - 1;
+    float sv[PER][KEEP + 1], wv[PER][TAPS], pg[PER];
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int i = threadIdx.x + k * 256;
+#pragma unroll
+      for (int j = 0; j < KEEP; ++j) sv[k][j] = i < W ? st[(size_t)i * KEEP + j] : 0.f;
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) wv[k][j] = i < W ? conv_w[(size_t)i * TAPS + j] : 0.f;
+      pg[k] = i < W ? pre_gain[i] : 0.f;
     }
-    acc = fmaf(w[keep], now, acc);
-    if (keep > 0) s[keep - 1] = now;
-    out[base + i] = from_f32<TO>(now + acc);
+    float y[PER];
+    float ss = post_add_regs<PER>(x, term, base, parts, part_stride, post_gain, post_eps, W, red, y);
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)W + pre_eps);
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int i = threadIdx.x + k * 256;
+      if (i < W) {
+        const float now = y[k] * inv * pg[k];
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < KEEP; ++j) {                  // oldest input first
+          acc = fmaf(wv[k][j], sv[k][j], acc);
+          if (j > 0) st[(size_t)i * KEEP + j - 1] = sv[k][j];
+        }
+        acc = fmaf(wv[k][KEEP], now, acc);
+        if (KEEP > 0) st[(size_t)i * KEEP + KEEP - 1] = now;
+        out[base + i] = from_f32<TO>(now + acc);
+      }
+    }
+  } else if constexpr (PER > 0) {
+    float y[PER];
+    float ss = post_add_regs<PER>(x, term, base, parts, part_stride, post_gain, post_eps, W, red, y);
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)W + pre_eps);
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int i = threadIdx.x + k * 256;
+      if (i < W) conv_one(y[k] * inv * pre_gain[i], conv_w + (size_t)i * taps, st + (size_t)i * keep, keep, out + base + i);
+    }
+  } else {
+    float ss = post_add(x, term, base, parts, part_stride, post_gain, post_eps, W, red);
+    ss = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)W + pre_eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x)
+      conv_one(x[i] * inv * pre_gain[i], conv_w + (size_t)i * taps, st + (size_t)i * keep, keep, out + base + i);
   }
 }
 
@@ -295,14 +402,20 @@ SLLM_EXPORT int sllm_post_add_norm(float* stream_, const float* term, int parts,
   SLLM_REQUIRE(h == nullptr || pre_gain != nullptr, "post_add_norm: a normed output needs its gain");
   SLLM_REQUIRE(term != nullptr || h != nullptr, "post_add_norm: nothing to do");
   if (T == 0) return SLLM_OK;
-  if (h == nullptr || h_dtype == SLLM_F32)
-    launch_kernel(post_add_norm_kernel<float>, (unsigned)T, 256, 0, stream, stream_, term, parts, part_stride, post_gain, post_eps,
-                  pre_gain, pre_eps, (float*)h, W);
-  else if (h_dtype == SLLM_BF16)
-    launch_kernel(post_add_norm_kernel<__nv_bfloat16>, (unsigned)T, 256, 0, stream, stream_, term, parts, part_stride, post_gain,
-                  post_eps, pre_gain, pre_eps, (__nv_bfloat16*)h, W);
+#define PAN(TO_, PER_)                                                                                                      \
+  launch_kernel(post_add_norm_kernel<TO_, PER_>, (unsigned)T, 256, 0, stream, stream_, term, parts, part_stride, post_gain, \
+                post_eps, pre_gain, pre_eps, (TO_*)h, W)
+#define PAN_W(TO_)                       \
+  if (W <= 1024) PAN(TO_, 4);            \
+  else if (W <= 2048) PAN(TO_, 8);       \
+  else if (W <= 4096) PAN(TO_, 16);      \
+  else PAN(TO_, 0)
+  if (h == nullptr || h_dtype == SLLM_F32) { PAN_W(float); }
+  else if (h_dtype == SLLM_BF16) { PAN_W(__nv_bfloat16); }
   else
     SLLM_REQUIRE(false, "post_add_norm: unknown dtype %d", h_dtype);
+#undef PAN_W
+#undef PAN
   return launch_status("post_add_norm");
 }
 
@@ -315,14 +428,26 @@ SLLM_EXPORT int sllm_post_add_norm_conv(float* stream_, const float* term, int p
   SLLM_REQUIRE(pre_gain != nullptr && conv_w != nullptr && out != nullptr, "post_add_norm_conv: the norm's gain, the taps and an output");
   SLLM_REQUIRE(taps == 1 || conv_state != nullptr, "post_add_norm_conv: %d taps need the requests' state rows", taps);
   if (T == 0) return SLLM_OK;
-  if (out_dtype == SLLM_F32)
-    launch_kernel(post_add_norm_conv_kernel<float>, (unsigned)T, 256, 0, stream, stream_, term, parts, part_stride, post_gain,
-                  post_eps, pre_gain, pre_eps, conv_w, taps, conv_state, seq_of_token, state_slots, (float*)out, W);
-  else if (out_dtype == SLLM_BF16)
-    launch_kernel(post_add_norm_conv_kernel<__nv_bfloat16>, (unsigned)T, 256, 0, stream, stream_, term, parts, part_stride,
-                  post_gain, post_eps, pre_gain, pre_eps, conv_w, taps, conv_state, seq_of_token, state_slots, (__nv_bfloat16*)out, W);
+#define PANC(TO_, PER_, TAPS_)                                                                                               \
+  launch_kernel(post_add_norm_conv_kernel<TO_, PER_, TAPS_>, (unsigned)T, 256, 0, stream, stream_, term, parts, part_stride, \
+                post_gain, post_eps, pre_gain, pre_eps, conv_w, taps, conv_state, seq_of_token, state_slots, (TO_*)out, W)
+#define PANC_T(TO_, PER_)                  \
+  if (taps == 2) PANC(TO_, PER_, 2);       \
+  else if (taps == 3) PANC(TO_, PER_, 3);  \
+  else if (taps == 4) PANC(TO_, PER_, 4);  \
+  else PANC(TO_, PER_, 0)
+#define PANC_W(TO_)                                 \
+  if (W <= 1024) { PANC_T(TO_, 4); }                \
+  else if (W <= 2048) { PANC_T(TO_, 8); }           \
+  else if (W <= 4096) { PANC_T(TO_, 16); }          \
+  else PANC(TO_, 0, 0)
+  if (out_dtype == SLLM_F32) { PANC_W(float); }
+  else if (out_dtype == SLLM_BF16) { PANC_W(__nv_bfloat16); }
   else
     SLLM_REQUIRE(false, "post_add_norm_conv: unknown dtype %d", out_dtype);
+#undef PANC_W
+#undef PANC_T
+#undef PANC
   return launch_status("post_add_norm_conv");
 }
 

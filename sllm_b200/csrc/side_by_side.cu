@@ -171,6 +171,82 @@ short_conv_vec4_kernel(const float* __restrict__ x, int ld, int off, const float
   }
 }
 
+// Long portions: a thread walks RUN consecutive tokens of its four channels with the last inputs in registers, so every
+// input row is loaded once instead of once per tap.  Where a run starts, and where the next token belongs to another
+// request, the window is read afresh (from the rows before, or from the request's state row).  Sums in the order of the
+// kernels above: the same bits.  grid (ceil(T / RUN), ceil(C / 512)).
+template <int MODE, int TAPS, typename TO, int RUN>
+__global__ void __launch_bounds__(128)
+short_conv_run_kernel(const float* __restrict__ x, int ld, int off, const float* __restrict__ w, const float* __restrict__ state,
+                      const int* __restrict__ seq_of_token, const int* __restrict__ q_start, const int* __restrict__ state_slots,
+                      TO* __restrict__ out, int C, int T) {
+  constexpr int KEEP = TAPS - 1;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t0 = blockIdx.x * RUN, c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (c >= C) return;
+  float wl[4 * TAPS];                                   // [channel][tap]
+#pragma unroll
+  for (int k = 0; k < TAPS; ++k) {
+    const float4 q = __ldg(reinterpret_cast<const float4*>(w + (size_t)c * TAPS) + k);
+    wl[4 * k] = q.x; wl[4 * k + 1] = q.y; wl[4 * k + 2] = q.z; wl[4 * k + 3] = q.w;
+  }
+  float win[KEEP + 1][4];                               // [older input, oldest first][channel]
+  float now[4] = {0.f, 0.f, 0.f, 0.f};
+  int seq_before = -1;
+#pragma unroll
+  for (int r = 0; r < RUN; ++r) {
+    const int t = t0 + r;
+    if (t >= T) break;
+    const int seq = seq_of_token[t];
+    if (seq != seq_before) {
+      const int first = q_start[seq];
+      const float* sp = state + ((size_t)state_slots[seq] * C + c) * KEEP;
+#pragma unroll
+      for (int k = 0; k < KEEP; ++k) {
+        const int src = t - KEEP + k;
+        if (src >= first) {
+          const float4 q = *reinterpret_cast<const float4*>(x + (size_t)src * ld + off + c);
+          win[k][0] = q.x; win[k][1] = q.y; win[k][2] = q.z; win[k][3] = q.w;
+        } else {
+          const int idx = KEEP - (first - src);         // the state row holds the KEEP inputs before `first`
+#pragma unroll
+          for (int i = 0; i < 4; ++i) win[k][i] = idx >= 0 ? sp[i * KEEP + idx] : 0.f;
+        }
+      }
+      seq_before = seq;
+    } else {
+#pragma unroll
+      for (int k = 0; k + 1 < KEEP; ++k)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) win[k][i] = win[k + 1][i];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (KEEP > 0) win[KEEP - 1][i] = now[i];
+    }
+    const float4 q = *reinterpret_cast<const float4*>(x + (size_t)t * ld + off + c);
+    now[0] = q.x; now[1] = q.y; now[2] = q.z; now[3] = q.w;
+    float y[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float acc = 0.f;
+#pragma unroll
+      for (int k = 0; k < KEEP; ++k) acc = fmaf(wl[i * TAPS + k], win[k][i], acc);
+      acc = fmaf(wl[i * TAPS + KEEP], now[i], acc);
+      y[i] = MODE == 0 ? sbs_silu(acc) : now[i] + acc;
+    }
+    if constexpr (sizeof(TO) == 4) {
+      *reinterpret_cast<float4*>(out + (size_t)t * C + c) = make_float4(y[0], y[1], y[2], y[3]);
+    } else {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(y[0], y[1]), hi = __floats2bfloat162_rn(y[2], y[3]);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(out + (size_t)t * C + c) = pk;
+    }
+  }
+}
+
 // grid (S, ceil(C / 256)): a thread per (request, channel) rewrites its state row in ascending order
 __global__ void __launch_bounds__(256)
 short_conv_state_kernel(const float* __restrict__ x, int ld, int off, int taps, float* __restrict__ state,
@@ -251,7 +327,22 @@ SLLM_EXPORT int sllm_short_conv(const float* x, int ld, int off, const float* w,
   const int own_state = (T == S && taps > 1) ? 1 : 0;
   const bool vec = taps >= 2 && taps <= 4 && C % 4 == 0 && ld % 4 == 0 && off % 4 == 0 && (uintptr_t)x % 16 == 0 &&
                    (uintptr_t)w % 16 == 0 && (uintptr_t)state % 16 == 0 && (uintptr_t)out % 16 == 0;
-  if (vec) {
+  constexpr int CONV_RUN = 8;
+  if (vec && !own_state && T >= CONV_RUN * S) {         // portions of eight tokens and more on average
+    const dim3 rgrid((unsigned)((T + CONV_RUN - 1) / CONV_RUN), (unsigned)((C / 4 + 127) / 128));
+#define RUNK(MODE_, TAPS_, TO_)                                                                                            \
+  launch_kernel(short_conv_run_kernel<MODE_, TAPS_, TO_, CONV_RUN>, rgrid, 128, 0, stream, x, ld, off, w, (const float*)state, \
+                seq_of_token, q_start, state_slots, (TO_*)out, C, T)
+#define RUN_TAPS(MODE_, TO_)                          \
+  if (taps == 2) RUNK(MODE_, 2, TO_);                 \
+  else if (taps == 3) RUNK(MODE_, 3, TO_);            \
+  else RUNK(MODE_, 4, TO_)
+    if (mode == 0) { RUN_TAPS(0, float); }
+    else if (out_dtype == SLLM_F32) { RUN_TAPS(1, float); }
+    else { RUN_TAPS(1, __nv_bfloat16); }
+#undef RUN_TAPS
+#undef RUNK
+  } else if (vec) {
     const dim3 vgrid((unsigned)T, (unsigned)((C / 4 + 127) / 128));
 #define VEC(MODE_, TAPS_, TO_)                                                                                              \
   launch_kernel(short_conv_vec4_kernel<MODE_, TAPS_, TO_>, vgrid, 128, 0, stream, x, ld, off, w, state, seq_of_token, q_start, \

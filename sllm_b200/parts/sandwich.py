@@ -99,6 +99,7 @@ class SandwichBlock:
     stack of partial sums) in float32; nothing is added into the stream before its norm."""
 
     ROLES = ("mixer", "mixer_norm", "mixer_post", "mixer_conv", "ffn", "ffn_norm", "ffn_post", "ffn_conv")
+    fuse_single_token = True      # norm and convolution in one kernel where every request brings one token (False: two, for comparison)
 
     def __init__(self, parts: dict):
         unknown = set(parts) - set(self.ROLES)
@@ -143,7 +144,7 @@ class SandwichBlock:
         if conv is None:
             return ops.post_add_norm(residual, term, pg, pe, norm.weight, norm.eps, norm.dtype)
         state = cache.states.get(name) if cache is not None else None
-        if residual.shape[0] == step.num_seqs and (state is not None or conv.taps == 1):
+        if self.fuse_single_token and residual.shape[0] == step.num_seqs and (state is not None or conv.taps == 1):
             # every request brings one token: one kernel, the normed row never leaves it
             return ops.post_add_norm_conv(residual, term, pg, pe, norm.weight, norm.eps, conv.weight, state, step, conv.dtype)
         return conv(ops.post_add_norm(residual, term, pg, pe, norm.weight, norm.eps, torch.float32), state, step)

@@ -262,7 +262,7 @@ def test_a_lender_of_latents_may_not_borrow():
 
 # ---- each mechanism alone: an operation or a part against the plain function ------------------------------------------
 
-@pytest.mark.parametrize("W", [50, 96, 1000])
+@pytest.mark.parametrize("W", [50, 96, 1000, 1500, 3000, 4500])     # the kernel keeps rows of up to 1,024, 2,048 and 4,096 channels in registers
 def test_norm_with_one_number_before_and_after_a_sublayer(dev, W):
     """The sublayer's term (whole, and as a stack of partial sums) is normed with one number, joins the stream, and the
     stream is normed with another number for the next reader; each half alone too."""
@@ -321,7 +321,7 @@ def test_input_convolution_across_portions_and_slots(dev, C, taps):
     assert taps == 1 or float(state[1].abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("W,taps", [(50, 3), (96, 4), (1000, 2), (24, 1), (40, 6)])
+@pytest.mark.parametrize("W,taps", [(50, 3), (96, 4), (1000, 2), (24, 1), (40, 6), (1500, 4), (3000, 3), (4500, 2)])
 def test_norm_and_convolution_in_one_kernel_for_single_tokens(dev, W, taps):
     """A block's read of the stream where every request brings one token: the term of the sublayer before joins the stream
     behind its norm, the stream is normed, and h + conv(h) comes back, all in one call; three requests decode side by side for
