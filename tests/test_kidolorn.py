@@ -74,7 +74,18 @@ ONE_TAP = {"architecture": "Kidolorn", "vocab": 90, "width": 64, "norm": {"eps":
 TWO_TAPS = {"architecture": "Kidolorn", "vocab": 120, "width": 72, "norm": {"eps": 1e-6}, "canon": {"taps": 2},
             "layers": [{"type": "lightning", "mixer": {"heads": 4, "dim": 32, "vdim": 16, "decay": _decays(4)}, "mlp": _moe(16, 5, 8, 1.0)},
                        {"type": "mingru", "mixer": {"width": 40}, "mlp": _dense(100, 1.0)}]}
-CONFIGS = {"A": (CONFIG_A, 16), "B": (CONFIG_B, 16), "odd": (ODD, 8), "one_tap": (ONE_TAP, 4), "two_taps": (TWO_TAPS, 32)}
+MID = {               # a few hundred channels, no power of two: the products' tensor-core forms at sizes between tiny and real
+    "architecture": "Kidolorn", "vocab": 1000, "width": 320, "norm": {"eps": 1e-5}, "canon": {"taps": 4},
+    "layers": [
+        {"type": "lightning", "mixer": {"heads": 5, "dim": 64, "vdim": 48, "decay": _decays(5, 0.6, 0.9999)}, "mlp": _moe(8, 3, 96, 2.0)},
+        {"type": "latent_attention", "mixer": _latent(5, 48, 16, 64, 80, 0.125, 20000.0), "mlp": _dense(768, 1.5)},
+        {"type": "mingru", "mixer": {"width": 448}, "mlp": _moe(8, 3, 96, 2.0)},
+        {"type": "latent_attention", "mixer": _latent(10, 24, 16, 32, 80, 0.16, 20000.0, kv_from=1), "mlp": _dense(768, 1.5)},
+        {"type": "mingru", "mixer": {"width": 448}, "mlp": None},
+        {"type": "lightning", "mixer": {"heads": 5, "dim": 64, "vdim": 48, "decay": _decays(5, 0.6, 0.9999)}, "mlp": _dense(512, 1.0)},
+    ],
+}
+CONFIGS = {"A": (CONFIG_A, 16), "B": (CONFIG_B, 16), "odd": (ODD, 8), "one_tap": (ONE_TAP, 4), "two_taps": (TWO_TAPS, 32), "mid": (MID, 16)}
 
 
 def _devices():
