@@ -419,6 +419,49 @@ def test_element_wise_recurrence_in_portions_and_slots(dev, C):
     assert float(cache.states["mingru"][2].abs().max()) > 0.0
 
 
+@pytest.mark.parametrize("C,n,more", [(44, 600, 0), (8, 257, 1), (132, 1100, 3), (30, 300, 0)])
+def test_element_wise_recurrence_and_convolution_over_a_long_portion(dev, C, n, more):
+    """Portions of hundreds of tokens take other forms of both kernels (many short runs of eight channels; a run of tokens a
+    thread): one request's long portion, alone or beside requests that bring a token each, then a second portion that goes on
+    from the state rows, against the plain functions over the whole sequence."""
+    import sllm_b200.ops as ops
+    rng = np.random.default_rng(C + n)
+    taps = 4
+    tail = 9
+    lens = [n + tail] + [2] * more
+    proj = [rng.standard_normal((m, 3 * C)) * np.array([1.0] * C + [1.5] * C + [1.0] * C) + np.array([-2.0] * C + [0.0] * (2 * C)) for m in lens]
+    wconv = rng.standard_normal((C, taps))
+    to = _to(dev)
+    state = torch.zeros((more + 2, C), dtype=torch.float32, device=dev)
+    cstate = torch.zeros((more + 2, C, taps - 1), dtype=torch.float32, device=dev)
+    slots = list(range(more, -1, -1))                                                 # the long request sits in the last row used
+    outs, convs = [[] for _ in lens], [[] for _ in lens]
+    at = [0] * len(lens)
+    for q in ([n] + [1] * more, [tail] + [1] * more):
+        step = _step(dev, q, slots, [a + b for a, b in zip(at, q)])
+        rows = np.concatenate([proj[i][at[i]:at[i] + q[i]] for i in range(len(lens))])
+        y = ops.mingru_scan(to(rows), (0, C, 2 * C), state, step, C, torch.float32).cpu().numpy()
+        z = ops.short_conv_add(to(rows[:, :C]), to(wconv), cstate, step, torch.float32).cpu().numpy()
+        r0 = 0
+        for i in range(len(lens)):
+            outs[i].append(y[r0:r0 + q[i]])
+            convs[i].append(z[r0:r0 + q[i]])
+            r0 += q[i]
+            at[i] += q[i]
+    for i, p in enumerate(proj):
+        zg = 1.0 / (1.0 + np.exp(-p[:, :C]))
+        cand = plain.mingru_candidate(p[:, C:2 * C])
+        S, want = np.zeros(C), []
+        for t in range(len(p)):
+            S = (1.0 - zg[t]) * S + zg[t] * cand[t]
+            g = p[t, 2 * C:]
+            want.append(S * g / (1.0 + np.exp(-g)))
+        np.testing.assert_allclose(np.concatenate(outs[i]), np.stack(want), rtol=3e-5, atol=3e-5)
+        np.testing.assert_allclose(np.concatenate(convs[i]), plain.input_convolution(p[:, :C], wconv), rtol=3e-5, atol=3e-5)
+        np.testing.assert_allclose(state[slots[i]].cpu().numpy(), S, rtol=3e-5, atol=3e-5)
+    assert float(state[more + 1].abs().max()) == 0.0 and float(cstate[more + 1].abs().max()) == 0.0
+
+
 def test_candidate_of_the_recurrence_has_two_branches():
     u = np.array([-30.0, -1.0, -1e-9, 0.0, 1e-9, 2.0])
     c = plain.mingru_candidate(u)
