@@ -469,7 +469,7 @@ def test_candidate_of_the_recurrence_has_two_branches():
     assert (np.diff(c) >= 0).all()                      # continuous and rising through zero
 
 
-@pytest.mark.parametrize("heads,dk,dv", [(1, 64, 64), (3, 16, 24), (5, 6, 10), (2, 130, 12), (90, 16, 16), (4, 32, 16)])
+@pytest.mark.parametrize("heads,dk,dv", [(1, 64, 64), (3, 16, 24), (5, 6, 10), (2, 130, 12), (90, 16, 16), (4, 32, 16), (2, 128, 128), (1, 256, 80), (3, 96, 160)])
 def test_linear_attention_with_a_fixed_decay_in_portions_and_slots(dev, heads, dk, dv):
     """S <- decay_h S + k v^T through the part's own `mix` and output projection.  The last head all but never forgets
     (0.9999) and the first forgets within a few tokens; the heads' outputs share ONE root mean square."""
