@@ -57,7 +57,8 @@ class CacheManager:
         self.padding_slot = self.max_requests
         self.needs = list(needs)
         self.groups: list[CacheGroup] = []
-        self.run_group: dict[int, int] = {}        # run -> group (owning runs)
+        self.run_group: dict[int, int] = {}        # run -> group of its first paged cache (owning runs)
+        self.run_paged: dict[int, dict[str, int]] = {}   # run -> name -> group, every paged cache it holds
         self.state_runs: dict[int, list[SlotState]] = {}
         by_need: dict[PagedKV, int] = {}
         for run, entry in enumerate(self.needs):
@@ -69,14 +70,18 @@ class CacheManager:
                     raise TypeError(f"run {run}: a run that borrows a cache may only own state slots beside it")
             for need in flatten_needs(what):
                 if isinstance(need, PagedKV):
-                    if run in self.run_group:
-                        raise TypeError(f"run {run}: a layer holds at most one paged cache")
+                    named = self.run_paged.setdefault(run, {})
+                    if need.name in named:
+                        raise TypeError(f"run {run}: two paged caches named {need.name!r}")
+                    if need.stride < 1 or (need.stride > 1 and need.window is not None):
+                        raise TypeError(f"run {run}: a cache of one entry per {need.stride} tokens cannot have a window")
                     if need not in by_need:
                         by_need[need] = len(self.groups)
                         self.groups.append(CacheGroup(need, [], None))
                     g = by_need[need]
                     self.groups[g].runs.append(run)
-                    self.run_group[run] = g
+                    self.run_group.setdefault(run, g)
+                    named[need.name] = g
                 elif isinstance(need, SlotState):
                     have = self.state_runs.setdefault(run, [])
                     if any(s.name == need.name for s in have):
@@ -100,8 +105,24 @@ class CacheManager:
         self._ever_used = [set() for _ in self.groups]
 
     # ---- arithmetic -------------------------------------------------------------
-    def pages_for(self, tokens: int) -> int:
+    def pages_for(self, tokens: int, group: int | None = None) -> int:
+        """Pages that hold ``tokens`` tokens of a request: in ``group`` (whose pages may hold one entry per several
+        tokens), or in a group with an entry per token."""
+        if group is not None:
+            tokens //= self.groups[group].need.stride
         return -(-tokens // self.page_size) if tokens > 0 else 0
+
+    def tokens_per_page(self, group: int) -> int:
+        return self.page_size * self.groups[group].need.stride
+
+    def token_room(self, req_id=None) -> int:
+        """How many tokens the request (or a new one) could hold with the pages it has and all that are free."""
+        req = self.requests.get(req_id) if req_id is not None else None
+        room = None
+        for gi, g in enumerate(self.groups):
+            n = ((len(req.tables[gi]) if req else 0) + g.pool.free_count) * self.tokens_per_page(gi)
+            room = n if room is None else min(room, n)
+        return room if room is not None else 1 << 62
 
     def _first_needed_page(self, g: CacheGroup, committed: int) -> int:
         """First page a query at position ``committed`` (the next one) still reads."""
@@ -113,7 +134,7 @@ class CacheManager:
         out = []
         for gi, g in enumerate(self.groups):
             have = len(req.tables[gi]) if req else 0
-            out.append(max(0, self.pages_for(total_tokens) - have))
+            out.append(max(0, self.pages_for(total_tokens, gi) - have))
         return out
 
     def can_reserve(self, req_id, total_tokens: int) -> bool:
@@ -125,8 +146,8 @@ class CacheManager:
 
     def fits_at_all(self, total_tokens: int) -> bool:
         """Could a request of this many tokens ever be held, with the pools empty?"""
-        n = self.pages_for(total_tokens)
-        for g in self.groups:
+        for gi, g in enumerate(self.groups):
+            n = self.pages_for(total_tokens, gi)
             need = n if g.need.window is None else min(n, self.pages_for(g.need.window) + 1)
             if need > g.pool.capacity:
                 return False
@@ -177,7 +198,7 @@ class CacheManager:
         req = self.requests[req_id]
         if total_tokens < req.num_tokens:
             raise ValueError("a request's token count cannot shrink")
-        if any(self.pages_for(total_tokens) > len(t) for t in req.tables):
+        if any(self.pages_for(total_tokens, gi) > len(t) for gi, t in enumerate(req.tables)):
             raise ValueError(f"request {req_id!r}: {total_tokens} tokens committed beyond its reserved pages")
         req.num_tokens = total_tokens
         for gi, g in enumerate(self.groups):
@@ -238,7 +259,8 @@ class CacheManager:
     def bytes_per_token(self, itemsize: int) -> int:
         """Sum over caching runs of 2 * kv heads * head size * itemsize
         (runtime/memory_planner.py:12-15)."""
-        return sum(len(g.runs) * (2 if g.need.values else 1) * g.need.num_kv_heads * g.need.head_dim * itemsize for g in self.groups)
+        return sum(-(-len(g.runs) * (2 if g.need.values else 1) * g.need.num_kv_heads * g.need.head_dim * itemsize // g.need.stride)
+                   for g in self.groups)
 
     def state_bytes_per_request(self) -> int:
         """Bytes of fixed-size float32 state each request holds in the mixers' slots (tables that others
@@ -258,7 +280,8 @@ class CacheManager:
         for gi, g in enumerate(self.groups):
             w = "all keys" if g.need.window is None else f"a window of {g.need.window}"
             what = "kv heads" if g.need.values else "latent vectors"
-            lines.append(f"group {gi}: {len(g.runs)} runs x {g.need.num_kv_heads} {what} of {g.need.head_dim}, {w}")
+            every = f", one entry per {g.need.stride} tokens" if g.need.stride > 1 else ""
+            lines.append(f"group {gi}: {len(g.runs)} runs x {g.need.num_kv_heads} {what} of {g.need.head_dim}, {w}{every}")
         if self.state_runs:
             lines.append(f"state slots: {len(self.state_runs)} runs, {self.state_bytes_per_request()} bytes per request")
         return lines
@@ -286,6 +309,9 @@ class CacheManager:
                 i = self.groups[gi].runs.index(src)
                 kv = self.kv_storage[gi][i]
                 cache.group, cache.k, cache.v = gi, kv[0], kv[1 if self.groups[gi].need.values else 0]
+                for name, gj in self.run_paged.get(src, {}).items():
+                    kvj = self.kv_storage[gj][self.groups[gj].runs.index(src)]
+                    cache.paged[name] = LayerCache(group=gj, k=kvj[0], v=kvj[1 if self.groups[gj].need.values else 0])
             if how == "borrow" and run in self.state_runs:
                 src = run                     # (a borrowing run with state of its own keeps it apart from the lender's)
             if src in self.state_runs:

@@ -68,9 +68,14 @@ class RunEntry:
     an earlier entry of the run list whose cache this run reads (it then writes
     none).  A layer may be named by several entries; each owns its cache unless
     it borrows one.
+
+    `reentry`: this run opens pass number `reentry` of a range of layers that runs several
+    times in a row: before it the stream receives the embedding output once more (passes after
+    the first, 0) and row `reentry` of the plan's pass vectors.
     """
     layer: int
     cache_from: int | None = None
+    reentry: int | None = None
 
 
 @dataclass(frozen=True)
@@ -89,6 +94,10 @@ class ModelPlan:
     position_name: str | None = None   # prefix of the position encoding's own tensors, if it has any
     ignored_names: tuple[str, ...] = ()  # tensors a checkpoint may carry that the model does not use (said once, in a warning)
     embedding_scale: float = 1.0       # the looked-up rows are multiplied by it as they enter the stream
+    embedding_norm: PartSpec | None = None   # a norm the looked-up rows pass before they enter the stream
+    embedding_norm_name: str | None = None
+    pass_vectors_name: str | None = None     # tensor [passes, hidden]: what a run with `reentry` = t adds to the stream
+    passes: int = 0
 
     def validate(self) -> None:
         from .errors import ConfigError
@@ -103,6 +112,8 @@ class ModelPlan:
             if not 0 <= e.layer < len(self.layers):
                 raise ConfigError(f"run_list[{i}] names layer {e.layer}, "
                                   f"the model has {len(self.layers)}")
+            if e.reentry is not None and not (self.pass_vectors_name and 0 <= e.reentry < self.passes):
+                raise ConfigError(f"run_list[{i}].reentry={e.reentry}: the plan has {self.passes} pass vectors")
             if e.cache_from is not None:
                 if not 0 <= e.cache_from < i:
                     raise ConfigError(f"run_list[{i}].cache_from={e.cache_from} must name an earlier entry")

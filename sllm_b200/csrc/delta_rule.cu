@@ -32,6 +32,8 @@
 //       channel: u = a*u = 0, d = alpha; the walk's form for this mode has no sum before the update.
 //   linear attention with one fixed decay per head (mode 3):  S <- decay_h S + k v^T;  o = S^T q  with q, k and v each
 //       through silu first: mode 2's walk with d = decay_h on every row.
+//   linear attention whose forget gate also writes (mode 4):  S <- diag(f) S + (1 - f) v^T;  o = S^T silu(q)  with
+//       f = lower + (1 - lower) sigmoid(z + bias) per key channel: mode 2's walk with d = f and k = 1 - f.
 //
 // A second kernel finishes the mixer's output: each head's o over its root mean square, times a gain,
 // times sigmoid(gate logit), in the compute dtype.
@@ -104,6 +106,7 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
         const bool in = tok && i < dk;
         k[q][m] = in ? __ldg(row + p.off_k + kh * dk + i) : 0.f;
         a[q][m] = (in && p.mode == 0) ? __ldg(row + p.off_a + h * dk + i) + __ldg(p.a_bias + h * dk + i) : 0.f;
+        if (p.mode == 4) a[q][m] = in ? __ldg(p.a_bias + h * dk + i) : 0.f;        // the gate's bias; k holds its logit
         d[q][m] = (in && (p.mode == 0 || p.mode == 2)) ? __ldg(dec + i) : 0.f;
         r[q][m] = in ? __ldg(row + p.off_r + kh * dk + i) : 0.f;
       }
@@ -173,6 +176,19 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
         }
 #pragma unroll
         for (int m = 0; m < VPL; ++m) v[q][m] *= sigmoidf_(v[q][m]);
+      } else if (p.mode == 4) {
+#pragma unroll
+        for (int m = 0; m < PER_LANE; ++m) {
+          const int i = lane + 32 * m;
+          if (i < DKP) {
+            const bool in = i < dk;
+            const float lo = in ? __ldg(p.a_log + h * dk + i) : 0.f;                 // the gate's lower bound
+            const float f = lo + (1.0f - lo) * sigmoidf_(k[q][m] + a[q][m]);
+            s_k[tt * DKP + i] = in ? 1.0f - f : 0.f;
+            s_d[tt * DKP + i] = in ? f : 0.f;
+            s_r[tt * DKP + i] = r[q][m] * sigmoidf_(r[q][m]);
+          }
+        }
       } else {
 #pragma unroll
         for (int m = 0; m < PER_LANE; ++m) {
@@ -355,10 +371,11 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
 }
 
 // out[t, h*dv + j] = o[t, h, j] / sqrt(mean_j(o[t, h, :]^2) + eps) * gain[h*dv + j] * act(gate[t, h*dv + j]), act the sigmoid
-// (gate_act 0) or z * sigmoid(z) (gate_act 1); a warp per (t, h).
+// (gate_act 0) or z * sigmoid(z) (gate_act 1), or no gate at all (gate_act 2: `proj` is not read); a warp per (t, h).
 template <typename TO>
 __global__ void delta_out_kernel(const float* __restrict__ o, const float* __restrict__ gain, const float* __restrict__ proj,
-                                 int ld, int off_g, float eps, TO* __restrict__ out, int rows, int H, int dv, int gate_act) {
+                                 int ld, int off_g, float eps, TO* __restrict__ out, int rows, int H, int dv, int gate_act,
+                                 int out_ld, int out_off) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -372,8 +389,8 @@ __global__ void delta_out_kernel(const float* __restrict__ o, const float* __res
   const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
   const float* g = proj + (size_t)t * ld + off_g + h * dv;
   for (int j = lane; j < dv; j += 32) {
-    const float gate = gate_act == 1 ? g[j] * sigmoidf_(g[j]) : sigmoidf_(g[j]);
-    out[(size_t)row * dv + j] = from_f32<TO>(x[j] * inv * gain[h * dv + j] * gate);
+    const float gate = gate_act == 2 ? 1.0f : (gate_act == 1 ? g[j] * sigmoidf_(g[j]) : sigmoidf_(g[j]));
+    out[(size_t)t * out_ld + out_off + h * dv + j] = from_f32<TO>(x[j] * inv * gain[h * dv + j] * gate);
   }
 }
 
@@ -381,7 +398,7 @@ __global__ void delta_out_kernel(const float* __restrict__ o, const float* __res
 template <typename TO>
 __global__ void __launch_bounds__(256)
 delta_out_wide_kernel(const float* __restrict__ o, const float* __restrict__ gain, const float* __restrict__ proj, int ld, int off_g,
-                      float eps, TO* __restrict__ out, int H, int dv, int gate_act) {
+                      float eps, TO* __restrict__ out, int H, int dv, int gate_act, int out_ld, int out_off) {
   __shared__ float red[33];
   pdl_launch_dependents();
   pdl_wait();
@@ -394,8 +411,8 @@ delta_out_wide_kernel(const float* __restrict__ o, const float* __restrict__ gai
   const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
   const float* g = proj + (size_t)t * ld + off_g + h * dv;
   for (int j = threadIdx.x; j < dv; j += blockDim.x) {
-    const float gate = gate_act == 1 ? g[j] * sigmoidf_(g[j]) : sigmoidf_(g[j]);
-    out[row * dv + j] = from_f32<TO>(x[j] * inv * gain[h * dv + j] * gate);
+    const float gate = gate_act == 2 ? 1.0f : (gate_act == 1 ? g[j] * sigmoidf_(g[j]) : sigmoidf_(g[j]));
+    out[(size_t)t * out_ld + out_off + h * dv + j] = from_f32<TO>(x[j] * inv * gain[h * dv + j] * gate);
   }
 }
 
@@ -518,27 +535,46 @@ SLLM_EXPORT int sllm_decay_linear_attention(const float* proj, int ld, int off_q
   return dispatch_delta_rule(p, S, stream);
 }
 
+// Linear attention whose forget gate also writes, over q | gate logit | v columns of `proj` [T, ld]: `f_bias` and `lower` [H*dk].
+SLLM_EXPORT int sllm_forget_gate_attention(const float* proj, int ld, int off_q, int off_f, int off_v, const float* f_bias,
+                                           const float* lower, float* state, const int* q_start, const int* state_slots,
+                                           float* out, int S, int H, int dk, int dv, int max_q, cudaStream_t stream) {
+  SLLM_REQUIRE(S >= 0 && H > 0 && H <= 65535, "forget_gate_attention: bad sizes S=%d H=%d", S, H);
+  SLLM_REQUIRE(sllm_delta_rule_supports(dk, dv), "forget_gate_attention: a head of %d key and %d value channels is outside 1..256 keys", dk, dv);
+  SLLM_REQUIRE(off_q >= 0 && off_f >= 0 && off_v >= 0 && off_q + H * dk <= ld && off_f + H * dk <= ld && off_v + H * dv <= ld,
+               "forget_gate_attention: columns outside the product's %d", ld);
+  if (S == 0) return SLLM_OK;
+  DeltaParams p;
+  p.proj = proj; p.decay = proj; p.a_bias = f_bias; p.state = state; p.q_start = q_start; p.state_slots = state_slots;
+  p.out = out; p.ld = ld; p.off_r = off_q; p.off_k = off_f; p.off_v = off_v; p.off_a = 0; p.H = H; p.dk = dk; p.dv = dv;
+  p.chunk = 1; p.max_q = max_q;
+  p.mode = 4; p.hdiv = 1; p.gates = nullptr; p.ldg = p.off_b = p.off_dt = 0; p.a_log = lower; p.dt_bias = nullptr;
+  p.r_scale = 1.f; p.inv_tau = 1.f;
+  return dispatch_delta_rule(p, S, stream);
+}
+
 SLLM_EXPORT int sllm_delta_out(const float* o, const float* gain, const float* proj, int ld, int off_g, float eps, void* out,
-                               int out_dtype, int T, int H, int dv, int gate_act, cudaStream_t stream) {
-  SLLM_REQUIRE(T >= 0 && H > 0 && dv > 0 && off_g >= 0 && off_g + H * dv <= ld, "delta_out: bad sizes T=%d H=%d dv=%d", T, H, dv);
+                               int out_dtype, int T, int H, int dv, int gate_act, int out_ld, int out_off, cudaStream_t stream) {
+  SLLM_REQUIRE(out_off >= 0 && out_off + H * dv <= out_ld, "delta_out: the output's columns lie outside its %d", out_ld);
+  SLLM_REQUIRE(T >= 0 && H > 0 && dv > 0 && (gate_act == 2 || (off_g >= 0 && off_g + H * dv <= ld)), "delta_out: bad sizes T=%d H=%d dv=%d", T, H, dv);
   if (T == 0) return SLLM_OK;
   const long rows = (long)T * H;
   if (dv >= 512) {                      // a warp would walk such a row sixteen times and more
     if (out_dtype == SLLM_F32)
-      launch_kernel(delta_out_wide_kernel<float>, (unsigned)rows, 256, 0, stream, o, gain, proj, ld, off_g, eps, (float*)out, H, dv, gate_act);
+      launch_kernel(delta_out_wide_kernel<float>, (unsigned)rows, 256, 0, stream, o, gain, proj, ld, off_g, eps, (float*)out, H, dv, gate_act, out_ld, out_off);
     else if (out_dtype == SLLM_BF16)
       launch_kernel(delta_out_wide_kernel<__nv_bfloat16>, (unsigned)rows, 256, 0, stream, o, gain, proj, ld, off_g, eps,
-                    (__nv_bfloat16*)out, H, dv, gate_act);
+                    (__nv_bfloat16*)out, H, dv, gate_act, out_ld, out_off);
     else
       SLLM_REQUIRE(false, "delta_out: unknown dtype %d", out_dtype);
     return launch_status("delta_out");
   }
   const int blocks = (int)((rows + 7) / 8);
   if (out_dtype == SLLM_F32)
-    launch_kernel(delta_out_kernel<float>, blocks, 256, 0, stream, o, gain, proj, ld, off_g, eps, (float*)out, (int)rows, H, dv, gate_act);
+    launch_kernel(delta_out_kernel<float>, blocks, 256, 0, stream, o, gain, proj, ld, off_g, eps, (float*)out, (int)rows, H, dv, gate_act, out_ld, out_off);
   else if (out_dtype == SLLM_BF16)
     launch_kernel(delta_out_kernel<__nv_bfloat16>, blocks, 256, 0, stream, o, gain, proj, ld, off_g, eps, (__nv_bfloat16*)out,
-                  (int)rows, H, dv, gate_act);
+                  (int)rows, H, dv, gate_act, out_ld, out_off);
   else
     SLLM_REQUIRE(false, "delta_out: unknown dtype %d", out_dtype);
   return launch_status("delta_out");

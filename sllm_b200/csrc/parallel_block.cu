@@ -254,6 +254,40 @@ __global__ void tanh_cols_kernel(const float* __restrict__ x, int ld, int col0, 
   }
 }
 
+// stream[t, c] += rows[t, c] + vec[c] (rows may be absent): what a range of layers that runs again takes in before a pass.
+__global__ void __launch_bounds__(256)
+add_rows_kernel(float* __restrict__ stream, const float* __restrict__ rows, const float* __restrict__ vec, size_t n, int W) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float v = stream[i];
+    if (rows != nullptr) v += rows[i];
+    if (vec != nullptr) v += vec[i % W];
+    stream[i] = v;
+  }
+}
+
+// Two norms of one row: out_a = x / sqrt(mean(x^2) + eps) * gain_a and out_b likewise with gain_b (out_b may be absent).
+// A CTA per row; the row's sum of squares is taken once, in an order that depends on the width alone.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+norm_pair_kernel(const float* __restrict__ stream, const float* __restrict__ gain_a, const float* __restrict__ gain_b, float eps,
+                 TO* __restrict__ out_a, TO* __restrict__ out_b, int W) {
+  __shared__ float red[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const float* x = stream + (size_t)blockIdx.x * W;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) ss = fmaf(x[c], x[c], ss);
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)W + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float v = x[c] * inv;
+    out_a[(size_t)blockIdx.x * W + c] = from_f32<TO>(v * gain_a[c]);
+    if (out_b != nullptr) out_b[(size_t)blockIdx.x * W + c] = from_f32<TO>(v * gain_b[c]);
+  }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
@@ -335,4 +369,29 @@ SLLM_EXPORT int sllm_tanh_cols(const float* x, int ld, int col0, int n, void* ou
     launch_kernel(tanh_cols_kernel<__nv_bfloat16>, blocks, 256, 0, stream_, x, ld, col0, n, (__nv_bfloat16*)out, T);
   else SLLM_REQUIRE(false, "tanh_cols: unknown dtype %d", out_dtype);
   return launch_status("tanh_cols");
+}
+
+SLLM_EXPORT int sllm_add_rows(float* stream, const float* rows, const float* vec, int T, int W, cudaStream_t stream_) {
+  SLLM_REQUIRE(T >= 0 && W > 0, "add_rows: bad sizes T=%d W=%d", T, W);
+  if (T == 0) return SLLM_OK;
+  const size_t n = (size_t)T * W;
+  size_t blocks = (n + 1023) / 1024;
+  if (blocks > 4096) blocks = 4096;
+  launch_kernel(add_rows_kernel, (unsigned)blocks, 256, 0, stream_, stream, rows, vec, n, W);
+  return launch_status("add_rows");
+}
+
+SLLM_EXPORT int sllm_norm_pair(const float* stream, const float* gain_a, const float* gain_b, float eps, void* out_a, void* out_b,
+                               int out_dtype, int T, int W, cudaStream_t stream_) {
+  SLLM_REQUIRE(T >= 0 && W > 0 && gain_a && out_a && ((gain_b == nullptr) == (out_b == nullptr)), "norm_pair: bad arguments T=%d W=%d", T, W);
+  if (T == 0) return SLLM_OK;
+  const int threads = W >= 2048 ? 256 : 128;
+  if (out_dtype == SLLM_F32)
+    launch_kernel(norm_pair_kernel<float>, T, threads, 0, stream_, stream, gain_a, gain_b, eps, (float*)out_a, (float*)out_b, W);
+  else if (out_dtype == SLLM_BF16)
+    launch_kernel(norm_pair_kernel<__nv_bfloat16>, T, threads, 0, stream_, stream, gain_a, gain_b, eps, (__nv_bfloat16*)out_a,
+                  (__nv_bfloat16*)out_b, W);
+  else
+    SLLM_REQUIRE(false, "norm_pair: unknown dtype %d", out_dtype);
+  return launch_status("norm_pair");
 }

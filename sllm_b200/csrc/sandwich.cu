@@ -263,7 +263,7 @@ mingru_scan_kernel(const float* __restrict__ proj, int ld, int off_z, int off_x,
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
 gated_clamp_act_kernel(const TI* __restrict__ gu, const float* __restrict__ dense, TO* __restrict__ out, int N, int E, int ff,
-                       int il, float limit, float alpha) {
+                       int il, float limit, float alpha, int act) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t t = blockIdx.x;
@@ -272,8 +272,13 @@ gated_clamp_act_kernel(const TI* __restrict__ gu, const float* __restrict__ dens
     float y = 0.f;
     if (w != 0.f) {
       const TI* p = gu + t * 2 * N + (size_t)(c / il) * 2 * il + c % il;
-      const float g = fminf(to_f32(p[0]), limit), u = fminf(fmaxf(to_f32(p[il]), -limit), limit);
-      y = g * sw_sigmoid(alpha * g) * (u + 1.0f) * w;
+      if (act == 1) {                              // silu(g) * u
+        const float g = to_f32(p[0]);
+        y = g * sw_sigmoid(g) * to_f32(p[il]) * w;
+      } else {
+        const float g = fminf(to_f32(p[0]), limit), u = fminf(fmaxf(to_f32(p[il]), -limit), limit);
+        y = g * sw_sigmoid(alpha * g) * (u + 1.0f) * w;
+      }
     }
     out[t * N + c] = from_f32<TO>(y);
   }
@@ -282,7 +287,7 @@ gated_clamp_act_kernel(const TI* __restrict__ gu, const float* __restrict__ dens
 // bfloat16 in and out, blocks of 8 (or a multiple): eight columns a thread, one 16-byte load each of gate and up
 __global__ void __launch_bounds__(256)
 gated_clamp_act_vec_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ dense, __nv_bfloat16* __restrict__ out,
-                           int N, int E, int ff, int il, float limit, float alpha) {
+                           int N, int E, int ff, int il, float limit, float alpha, int act) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t t = blockIdx.x;
@@ -298,6 +303,10 @@ gated_clamp_act_vec_kernel(const __nv_bfloat16* __restrict__ gu, const float* __
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         float2 g = __bfloat1622float2(g2[k]), u = __bfloat1622float2(u2[k]);
+        if (act == 1) {
+          r2[k] = __floats2bfloat162_rn(g.x * sw_sigmoid(g.x) * u.x * w, g.y * sw_sigmoid(g.y) * u.y * w);
+          continue;
+        }
         g.x = fminf(g.x, limit); g.y = fminf(g.y, limit);
         u.x = fminf(fmaxf(u.x, -limit), limit); u.y = fminf(fmaxf(u.y, -limit), limit);
         r2[k] = __floats2bfloat162_rn(g.x * sw_sigmoid(alpha * g.x) * (u.x + 1.0f) * w, g.y * sw_sigmoid(alpha * g.y) * (u.y + 1.0f) * w);
@@ -311,7 +320,7 @@ constexpr int RS_WARPS = 4;
 
 // a warp per token
 __global__ void __launch_bounds__(RS_WARPS * 32)
-moe_route_top_softmax_kernel(const float* __restrict__ logits, int T, int E, int top, float* __restrict__ dense,
+moe_route_top_softmax_kernel(const float* __restrict__ logits, int T, int E, int top, float scale, float* __restrict__ dense,
                              int* __restrict__ idx, float* __restrict__ wts) {
   extern __shared__ float sm[];
   pdl_launch_dependents();
@@ -351,7 +360,7 @@ moe_route_top_softmax_kernel(const float* __restrict__ logits, int T, int E, int
     }
     __syncwarp();
   }
-  const float inv = 1.0f / sum;
+  const float inv = scale / sum;
   if (lane == 0)
     for (int n = 0; n < top; ++n) {
       const float w = wts[(size_t)t * top + n] * inv;
@@ -476,7 +485,7 @@ SLLM_EXPORT int sllm_mingru_scan(const float* proj, int ld, int off_z, int off_x
 }
 
 SLLM_EXPORT int sllm_gated_clamp_act(const void* gu, int in_dtype, const float* dense, void* out, int out_dtype, int T, int N, int E,
-                                     int ff, int interleave, float limit, float alpha, cudaStream_t stream) {
+                                     int ff, int interleave, float limit, float alpha, int act, cudaStream_t stream) {
   SLLM_REQUIRE(T >= 0 && N >= 1 && ff >= 1 && interleave >= 1 && N % interleave == 0, "gated_clamp_act: bad sizes T=%d N=%d ff=%d blocks of %d",
                T, N, ff, interleave);
   SLLM_REQUIRE(dense == nullptr || (E >= 1 && (long)E * ff == N && ff % interleave == 0),
@@ -487,14 +496,14 @@ SLLM_EXPORT int sllm_gated_clamp_act(const void* gu, int in_dtype, const float* 
     int by = (N / 8 + 255) / 256;
     if (by > 64) by = 64;
     launch_kernel(gated_clamp_act_vec_kernel, dim3((unsigned)T, (unsigned)by), 256, 0, stream, (const __nv_bfloat16*)gu, dense,
-                  (__nv_bfloat16*)out, N, E, ff, interleave, limit, alpha);
+                  (__nv_bfloat16*)out, N, E, ff, interleave, limit, alpha, act);
     return launch_status("gated_clamp_act");
   }
   int by = (N + 255) / 256;
   if (by > 64) by = 64;
   const dim3 grid((unsigned)T, (unsigned)by);
 #define LAUNCH(TI, TO) \
-  launch_kernel(gated_clamp_act_kernel<TI, TO>, grid, 256, 0, stream, (const TI*)gu, dense, (TO*)out, N, E, ff, interleave, limit, alpha)
+  launch_kernel(gated_clamp_act_kernel<TI, TO>, grid, 256, 0, stream, (const TI*)gu, dense, (TO*)out, N, E, ff, interleave, limit, alpha, act)
   if (in_dtype == SLLM_F32 && out_dtype == SLLM_F32) LAUNCH(float, float);
   else if (in_dtype == SLLM_F32 && out_dtype == SLLM_BF16) LAUNCH(float, __nv_bfloat16);
   else if (in_dtype == SLLM_BF16 && out_dtype == SLLM_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
@@ -503,14 +512,14 @@ SLLM_EXPORT int sllm_gated_clamp_act(const void* gu, int in_dtype, const float* 
   return launch_status("gated_clamp_act");
 }
 
-SLLM_EXPORT int sllm_moe_route_top_softmax(const float* logits, int T, int E, int top, float* dense, int* idx, float* wts,
+SLLM_EXPORT int sllm_moe_route_top_softmax(const float* logits, int T, int E, int top, float scale, float* dense, int* idx, float* wts,
                                            cudaStream_t stream) {
   SLLM_REQUIRE(T >= 0 && E >= 1 && top >= 1 && top <= E, "moe_route_top_softmax: bad sizes T=%d E=%d top=%d", T, E, top);
   const size_t smem = (size_t)RS_WARPS * E * sizeof(float);
   SLLM_REQUIRE(smem <= 48 * 1024, "moe_route_top_softmax: %d experts are more than the kernel keeps in shared memory", E);
   if (T == 0) return SLLM_OK;
   launch_kernel(moe_route_top_softmax_kernel, (unsigned)((T + RS_WARPS - 1) / RS_WARPS), RS_WARPS * 32, smem, stream, logits, T, E,
-                top, dense, idx, wts);
+                top, scale, dense, idx, wts);
   return launch_status("moe_route_top_softmax");
 }
 

@@ -5,6 +5,8 @@
 //                           square times a gain shared by the heads, then rotated (the first `rot` channels, channel i
 //                           with i + rot/2, by the table's cos and sin of the token's position); values as they are.
 //                           Queries leave in the compute dtype, keys and values go to their token's place in the pages.
+//                           Without gains the heads are not normed; `q_mul` (one number per query head) multiplies the
+//                           query head (a factor on its scores).
 //                           Key and value sizes may differ: the cache's head is D >= both, the rest is zeros.
 //   short_conv_silu         y[t, c] = silu(sum_j w[c, taps-1-j] x[t-j, c]) over a request's own tokens; the taps-1 inputs
 //                           before a portion come from the request's state row, zeros before the sequence starts.
@@ -21,7 +23,8 @@ __device__ __forceinline__ float sbs_silu(float z) { return z / (1.0f + expf(-z)
 template <typename TC>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_kv_write_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ q_gain,
-                             const float* __restrict__ k_gain, float eps, const int* __restrict__ positions,
+                             const float* __restrict__ k_gain, const float* __restrict__ q_mul, float eps,
+                             const int* __restrict__ positions,
                              const float* __restrict__ table, int rot, int max_pos, int nq, int nkv, int dim, int vdim, int D,
                              const int* __restrict__ slot_mapping, int page_size, int num_pages, TC* __restrict__ k_cache,
                              TC* __restrict__ v_cache, TC* __restrict__ q_out, int T) {
@@ -51,23 +54,27 @@ qk_norm_rope_kv_write_kernel(const float* __restrict__ qkv, int ld, const float*
   }
   const float* x = row + (size_t)head * dim;
   const float* gain = head < nq ? q_gain : k_gain;
-  float ss = 0.f;
-  for (int d = lane; d < dim; d += 32) ss = fmaf(x[d], x[d], ss);
-  ss = warp_sum(ss);
-  const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+  float inv = 1.0f;
+  if (gain != nullptr) {
+    float ss = 0.f;
+    for (int d = lane; d < dim; d += 32) ss = fmaf(x[d], x[d], ss);
+    ss = warp_sum(ss);
+    inv = 1.0f / sqrtf(ss / (float)dim + eps);
+  }
+  if (head < nq && q_mul != nullptr) inv *= q_mul[head];
   const int half = rot / 2;
   if (rot > 0) {
     int pos = positions[t];
     pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
     const float* cs = table + (size_t)pos * rot;                    // cos[half] then sin[half]
     for (int j = lane; j < half; j += 32) {
-      const float u = x[j] * inv * gain[j], v = x[j + half] * inv * gain[j + half];
+      const float u = x[j] * inv * (gain ? gain[j] : 1.f), v = x[j + half] * inv * (gain ? gain[j + half] : 1.f);
       const float c = cs[j], sn = cs[half + j];
       dst[j] = from_f32<TC>(u * c - v * sn);
       dst[j + half] = from_f32<TC>(v * c + u * sn);
     }
   }
-  for (int d = rot + lane; d < D; d += 32) dst[d] = from_f32<TC>(d < dim ? x[d] * inv * gain[d] : 0.f);
+  for (int d = rot + lane; d < D; d += 32) dst[d] = from_f32<TC>(d < dim ? x[d] * inv * (gain ? gain[d] : 1.f) : 0.f);
 }
 
 // grid (T, ceil(C / 256)): a thread per (token, channel).  MODE 0: silu of the convolution; MODE 1: the input plus its
@@ -288,10 +295,11 @@ norm_mean_add_kernel(float* __restrict__ stream, const float* __restrict__ a, co
 
 using namespace sllm;
 
-SLLM_EXPORT int sllm_qk_norm_rope_kv_write(const float* qkv, int ld, const float* q_gain, const float* k_gain, float eps,
+SLLM_EXPORT int sllm_qk_norm_rope_kv_write(const float* qkv, int ld, const float* q_gain, const float* k_gain, const float* q_mul, float eps,
                                            const int* positions, const float* table, int rot, int max_pos, int nq, int nkv,
                                            int dim, int vdim, int D, const int* slot_mapping, int page_size, int num_pages,
                                            void* k_cache, void* v_cache, void* q_out, int cache_dtype, int T, cudaStream_t stream) {
+  SLLM_REQUIRE((q_gain == nullptr) == (k_gain == nullptr), "qk_norm_rope: query and key heads are normed together or not at all");
   SLLM_REQUIRE(T >= 0 && nq > 0 && nkv > 0 && dim > 0 && vdim > 0, "qk_norm_rope: bad sizes T=%d nq=%d nkv=%d dim=%d vdim=%d", T, nq, nkv, dim, vdim);
   SLLM_REQUIRE(D >= dim && D >= vdim, "qk_norm_rope: the cache's head of %d is smaller than a key of %d or a value of %d", D, dim, vdim);
   SLLM_REQUIRE(ld >= (nq + nkv) * dim + nkv * vdim, "qk_norm_rope: the product's %d columns are fewer than q|k|v", ld);
@@ -302,7 +310,7 @@ SLLM_EXPORT int sllm_qk_norm_rope_kv_write(const float* qkv, int ld, const float
   const long items = (long)T * (nq + 2 * nkv);
   const unsigned blocks = (unsigned)((items + 3) / 4);
 #define LAUNCH(TC)                                                                                                        \
-  launch_kernel(qk_norm_rope_kv_write_kernel<TC>, blocks, 128, 0, stream, qkv, ld, q_gain, k_gain, eps, positions, table, rot, \
+  launch_kernel(qk_norm_rope_kv_write_kernel<TC>, blocks, 128, 0, stream, qkv, ld, q_gain, k_gain, q_mul, eps, positions, table, rot, \
                 max_pos, nq, nkv, dim, vdim, D, slot_mapping, page_size, num_pages, (TC*)k_cache, (TC*)v_cache, (TC*)q_out, T)
   if (cache_dtype == SLLM_F32) LAUNCH(float);
   else if (cache_dtype == SLLM_BF16) LAUNCH(__nv_bfloat16);

@@ -99,7 +99,15 @@ def pack(layout: BatchLayout, h: np.ndarray, cache, entries, totals, *, tokens_f
             if bt is not None:
                 bt[si, :m] = table
                 bt[si, m:] = -1
-            if n == 1:
+            stride = cache.groups[gi].need.stride
+            if stride > 1:
+                # one entry per block of `stride` positions: the token that completes block b writes entry b
+                p = np.arange(tot - n, tot, dtype=np.int64)
+                ends = (p + 1) % stride == 0
+                entry = np.where(ends, (p + 1) // stride - 1, 0)
+                pages = np.asarray(table, dtype=np.int64)[entry // ps] if len(table) else np.zeros(n, dtype=np.int64)
+                maps[gi][t0:t0 + n] = np.where(ends, pages * ps + entry % ps, -1).astype(np.int32)
+            elif n == 1:
                 page = table[(tot - 1) // ps]
                 if page < 0:
                     raise RuntimeError(f"request {e.req_id!r}: a token would be written to a page given back")
@@ -151,6 +159,6 @@ def pages_missing(cache, entries, totals) -> list[int]:
         need = 0
         for e, tot in zip(entries, totals):
             req = cache.requests.get(e.req_id)
-            need += max(0, cache.pages_for(tot) - (len(req.tables[gi]) if req else 0))
+            need += max(0, cache.pages_for(tot, gi) - (len(req.tables[gi]) if req else 0))
         out.append(need)
     return out

@@ -166,7 +166,7 @@ class Scheduler:
             n = min(r.pending, self.chunk_size, budget)
             if self.policy == "on_demand" and self.cache.groups:
                 # start with the pages there are; the rest of the prompt follows as they come free
-                n = min(n, min(g.pool.free_count for g in self.cache.groups) * self.cache.page_size)
+                n = min(n, self.cache.token_room())
             total = len(r.prompt) + r.params.max_new if self.policy == "reserve" else r.num_computed + n
             if n <= 0 or not self.cache.can_reserve(r.req_id, total):
                 skipped.append(r)
@@ -233,9 +233,7 @@ class Scheduler:
             raise RuntimeError(f"request {r.req_id!r} was admitted with its pages reserved and lacks them")
         if n > 1:
             # a prompt portion: shorten it to the pages there are
-            held = min(len(t) for t in cache.requests[r.req_id].tables) if cache.groups else 0
-            free = min(g.pool.free_count for g in cache.groups) if cache.groups else 0
-            n = min(n, (held + free) * cache.page_size - r.num_computed)
+            n = min(n, cache.token_room(r.req_id) - r.num_computed) if cache.groups else n
             if n > 0:
                 cache.reserve(r.req_id, r.num_computed + n)
             return max(n, 0)

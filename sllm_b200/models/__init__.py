@@ -1,5 +1,5 @@
 """Architectures.  Importing this package registers each of them."""
-from . import kidolorn, nutopel, qwen2, rososun  # noqa: F401
+from . import gerupel, kidolorn, nutopel, qwen2, rososun  # noqa: F401
 from .causal_lm import CausalLM
 
-__all__ = ["CausalLM", "kidolorn", "nutopel", "qwen2", "rososun"]
+__all__ = ["CausalLM", "gerupel", "kidolorn", "nutopel", "qwen2", "rososun"]

@@ -52,6 +52,8 @@ class CausalLM:
         kw = dict(dtype=dtype, device=self.device)
         self.layers = [Layer(s, **kw) for s in plan.layers]
         self.final_norm = NORMS.build(plan.final_norm, **kw)
+        self.embedding_norm = NORMS.build(plan.embedding_norm, **kw) if plan.embedding_norm is not None else None
+        self.pass_vectors = None   # [passes, H] float32
         self.position = POSITIONS.build(plan.position, **kw) if plan.position is not None else None
         self.embedding = None      # [V, H] compute dtype
         self.head = None           # [V, H] compute dtype (the embedding itself when tied)
@@ -62,6 +64,8 @@ class CausalLM:
         for layer in self.layers:
             out.extend(layer.named_parts())
         out.append((self.plan.final_norm_name, self.final_norm))
+        if self.embedding_norm is not None:
+            out.append((self.plan.embedding_norm_name, self.embedding_norm))
         if self.position is not None and self.plan.position_name:
             out.append((self.plan.position_name, self.position))
         return out
@@ -73,6 +77,8 @@ class CausalLM:
             specs.extend(s.prefixed(prefix) for s in part.tensor_specs())
         if p.head_name is not None:
             specs.append(TensorSpec(p.head_name, (p.vocab_size, p.hidden_size), role="matrix"))
+        if p.pass_vectors_name is not None:
+            specs.append(TensorSpec(p.pass_vectors_name, (p.passes, p.hidden_size), role="bias"))
         return specs
 
     def ignored_tensor_names(self):
@@ -84,6 +90,8 @@ class CausalLM:
         self.embedding = fetch(p.embedding_name).to(device=self.device, dtype=self.dtype).contiguous()
         for prefix, part in self._named_parts():
             part.bind(lambda rel, _p=prefix: fetch(join_name(_p, rel)))
+        if p.pass_vectors_name is not None:
+            self.pass_vectors = fetch(p.pass_vectors_name).to(device=self.device, dtype=torch.float32).contiguous()
         if p.head_name is None:
             self.head = self.embedding
         else:
@@ -119,10 +127,18 @@ class CausalLM:
         residual = ops.embed_gather(self.embedding, step.token_ids, self.plan.embedding_scale)       # [T, H] float32
         if self.position is not None:
             self.position.on_embedding(residual, step)
+        entered = None
+        if self.embedding_norm is not None:
+            # the normed rows are the stream's start; a range of layers that runs again takes them in once more
+            entered = self.embedding_norm.add_norm(residual, None, out_dtype=torch.float32)
+            residual = entered.clone() if any(e.reentry for e in self.plan.run_list) else entered
         delta = None
         runs = self.plan.run_list
         for i, e in enumerate(runs):
             block = self.layers[e.layer].block
+            if e.reentry is not None:
+                # (a term the run before left pending is added by this block's norm; sums commute)
+                ops.add_rows_(residual, entered if e.reentry > 0 else None, self.pass_vectors[e.reentry])
             kw = {}
             if getattr(block, "accepts_next_norm", False) and i + 1 < len(runs):
                 # the norm that reads the stream next: this block's last product may prepare its input

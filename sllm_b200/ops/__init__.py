@@ -203,18 +203,64 @@ def delta_rule(proj, offs, decay, a_bias, state, step, heads: int, dk: int, dv: 
     return out
 
 
-GATE_ACTS = {"sigmoid": 0, "silu": 1}
+GATE_ACTS = {"sigmoid": 0, "silu": 1, "none": 2}
 
 
-def delta_out(o, gain, proj, off_g: int, eps: float, heads: int, dv: int, out_dtype, gate_act: str = "sigmoid") -> torch.Tensor:
+def delta_out(o, gain, proj, off_g: int, eps: float, heads: int, dv: int, out_dtype, gate_act: str = "sigmoid", out=None,
+              out_off: int = 0) -> torch.Tensor:
     """Each head's ``o`` over its root mean square, times ``gain`` (``[heads*dv]``), times ``sigmoid`` (or ``silu``) of
-    the gate logits (columns ``off_g`` of ``proj``), in ``out_dtype``."""
-    _chk(o, gain, proj)
+    the gate logits (columns ``off_g`` of ``proj``), in ``out_dtype``; with ``gate_act`` ``none`` there is no gate and
+    ``proj`` may be None.  ``out``: a wider tensor whose columns ``out_off ..`` receive the result."""
+    if gate_act == "none":
+        proj, off_g = o, 0
+    _chk(o, gain, proj, out)
     T = o.shape[0]
-    out = torch.empty((T, heads * dv), dtype=out_dtype, device=o.device)
-    call("sllm_delta_out", _p(o), _p(gain), _p(proj), proj.shape[1], int(off_g), float(eps), _p(out), _dtc(out_dtype), T, heads, dv,
-         GATE_ACTS[gate_act], _stream())
+    if out is None:
+        out = torch.empty((T, heads * dv), dtype=out_dtype, device=o.device)
+    call("sllm_delta_out", _p(o), _p(gain), _p(proj), proj.shape[1], int(off_g), float(eps), _p(out), _dtc(out.dtype), T, heads, dv,
+         GATE_ACTS[gate_act], out.shape[1], int(out_off), _stream())
     return out
+
+
+def forget_gate_attention(proj, offs, f_bias, lower, state, step, heads: int, dk: int, dv: int) -> torch.Tensor:
+    """S <- diag(f) S + (1 - f) v^T; o = S^T silu(q) with f = lower + (1 - lower) sigmoid(z + f_bias) per key channel, over the
+    step's tokens from and into ``state`` (float32 ``[slots, heads, dk, dv]``).  ``proj`` float32 ``[T, ld]`` holds q, the
+    gate's logits z and v at columns ``offs``; ``f_bias`` and ``lower`` float32 ``[heads*dk]``.  Returns ``o`` float32
+    ``[T, heads*dv]``."""
+    _chk(proj, f_bias, lower, state)
+    T, ld = proj.shape
+    if proj.dtype != torch.float32 or state.dtype != torch.float32 or f_bias.dtype != torch.float32 or lower.dtype != torch.float32:
+        raise KernelError("forget_gate_attention: everything that enters the recurrence is float32")
+    if tuple(state.shape[1:]) != (heads, dk, dv) or f_bias.numel() != heads * dk or lower.numel() != heads * dk:
+        raise KernelError(f"forget_gate_attention: state {tuple(state.shape)} or the gate's vectors do not fit {heads} heads of {dk}x{dv}")
+    out = torch.empty((T, heads * dv), dtype=torch.float32, device=proj.device)
+    off_q, off_f, off_v = (int(o) for o in offs)
+    call("sllm_forget_gate_attention", _p(proj), ld, off_q, off_f, off_v, _p(f_bias), _p(lower), _p(state), _p(step.q_start),
+         _p(step.state_slots), _p(out), step.num_seqs, heads, dk, dv, int(step.max_q_len), _stream())
+    return out
+
+
+def add_rows_(stream, rows, vec) -> None:
+    """``stream += rows + vec`` in place: ``rows`` float32 ``[T, W]`` or None, ``vec`` float32 ``[W]`` or None."""
+    _chk(stream, rows, vec)
+    T, W = stream.shape
+    if stream.dtype != torch.float32 or (rows is not None and (rows.dtype != torch.float32 or tuple(rows.shape) != (T, W))) or \
+            (vec is not None and (vec.dtype != torch.float32 or vec.numel() != W)):
+        raise KernelError("add_rows_: the stream, the rows and the vector are float32 of the stream's width")
+    call("sllm_add_rows", _p(stream), _p(rows), _p(vec), T, W, _stream())
+
+
+def norm_pair(stream, gain_a, gain_b, eps: float, out_dtype):
+    """Two RMS norms of the same float32 rows: ``(x / rms(x) * gain_a, x / rms(x) * gain_b)`` in ``out_dtype`` (the second
+    None when ``gain_b`` is None)."""
+    _chk(stream, gain_a, gain_b)
+    T, W = stream.shape
+    if stream.dtype != torch.float32 or gain_a.dtype != torch.float32 or (gain_b is not None and gain_b.dtype != torch.float32):
+        raise KernelError("norm_pair: the stream and the gains are float32")
+    a = torch.empty((T, W), dtype=out_dtype, device=stream.device)
+    b = torch.empty((T, W), dtype=out_dtype, device=stream.device) if gain_b is not None else None
+    call("sllm_norm_pair", _p(stream), _p(gain_a), _p(gain_b), float(eps), _p(a), _p(b), _dtc(out_dtype), T, W, _stream())
+    return a, b
 
 
 def gated_delta_rule(qkv, offs, gates, off_b: int, off_dt: int, a_log, dt_bias, state, step, heads: int, key_heads: int,
@@ -259,12 +305,13 @@ def gated_linear_attention(proj, offs, z, state, step, heads: int, dk: int, dv: 
 # ---- two mixers side by side: normed, rotated attention heads; short convolutions; the normed mean ---------------
 
 def qk_norm_rope_kv_write(qkv, q_gain, k_gain, eps: float, positions, table, rotary_dim: int, nq: int, nkv: int, dim: int,
-                          vdim: int, slot_mapping, k_cache, v_cache, out_dtype) -> torch.Tensor:
+                          vdim: int, slot_mapping, k_cache, v_cache, out_dtype, q_mul=None) -> torch.Tensor:
     """From a float32 product ``[T, (nq+nkv)*dim + nkv*vdim]``: every query and key head over its root mean square times
     its gain (``[dim]``, shared by the heads), then rotated; values as they are.  The queries come back ``[T, nq*D]`` in
     ``out_dtype`` with D the cache's head size (>= dim and vdim; zeros beyond); keys and values go to ``slot_mapping`` in
-    the pages (not written when ``slot_mapping`` is None)."""
-    _chk(qkv, q_gain, k_gain, positions, table, slot_mapping, k_cache, v_cache)
+    the pages (not written when ``slot_mapping`` is None).  With both gains None the heads are not normed; ``q_mul``
+    (float32 ``[nq]``) multiplies each query head."""
+    _chk(qkv, q_gain, k_gain, q_mul, positions, table, slot_mapping, k_cache, v_cache)
     T, ld = qkv.shape
     num_pages, nkv_c, page_size, D = k_cache.shape
     if qkv.dtype != torch.float32 or nkv_c != nkv or k_cache.dtype != out_dtype or tuple(v_cache.shape) != tuple(k_cache.shape):
@@ -275,7 +322,7 @@ def qk_norm_rope_kv_write(qkv, q_gain, k_gain, eps: float, positions, table, rot
             raise KernelError("qk_norm_rope_kv_write: rotary table must be float32 [positions, 2, rotary_dim/2]")
         max_pos = table.shape[0]
     q = torch.empty((T, nq * D), dtype=out_dtype, device=qkv.device)
-    call("sllm_qk_norm_rope_kv_write", _p(qkv), ld, _p(q_gain), _p(k_gain), float(eps), _p(positions), _p(table), int(rotary_dim),
+    call("sllm_qk_norm_rope_kv_write", _p(qkv), ld, _p(q_gain), _p(k_gain), _p(q_mul), float(eps), _p(positions), _p(table), int(rotary_dim),
          max_pos, nq, nkv, dim, vdim, D, _p(slot_mapping), page_size, num_pages, _p(k_cache), _p(v_cache), _p(q),
          _dtc(out_dtype), T, _stream())
     return q
@@ -356,9 +403,9 @@ def moe_act(up, dense, ff: int, out_dtype) -> torch.Tensor:
     return out
 
 
-def moe_route_top_softmax(logits, top: int):
+def moe_route_top_softmax(logits, top: int, scale: float = 1.0):
     """The ``top`` largest of the float32 router logits ``[T, E]`` win (the lower index on a tie); their weights are the
-    softmax over the winners alone.  (dense weights float32 ``[T, E]`` with zeros elsewhere, indices int32 ``[T, top]`` by
+    softmax over the winners alone, times ``scale``.  (dense weights float32 ``[T, E]`` with zeros elsewhere, indices int32 ``[T, top]`` by
     falling logit, weights float32 ``[T, top]``)."""
     _chk(logits)
     T, E = logits.shape
@@ -367,22 +414,24 @@ def moe_route_top_softmax(logits, top: int):
     dense = torch.empty((T, E), dtype=torch.float32, device=logits.device)
     idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     wts = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-    call("sllm_moe_route_top_softmax", _p(logits), T, E, int(top), _p(dense), _p(idx), _p(wts), _stream())
+    call("sllm_moe_route_top_softmax", _p(logits), T, E, int(top), float(scale), _p(dense), _p(idx), _p(wts), _stream())
     return dense, idx, wts
 
 
-def gated_clamp_act(gu, interleave: int, limit: float, out_dtype, *, alpha: float = 1.702, dense=None, ff: int | None = None):
+def gated_clamp_act(gu, interleave: int, limit: float, out_dtype, *, alpha: float = 1.702, dense=None, ff: int | None = None,
+                    act: str = "clamped_swish"):
     """``g' sigmoid(alpha g') (u' + 1)`` with ``g' = min(g, limit)`` and ``u' = clamp(u, -limit, limit)`` of ``gu [T, 2N]``
     whose columns alternate between gate and up in blocks of ``interleave``.  With ``dense`` (float32 ``[T, E]``, the
     routing weights of E experts of ``ff`` columns each, N = E ff): also times the token's weight of the column's expert;
-    the columns of an expert a token does not use are not read."""
+    the columns of an expert a token does not use are not read.  ``act`` ``silu``: ``g sigmoid(g) u`` instead (``limit`` and
+    ``alpha`` unused)."""
     _chk(gu, dense)
     T, two_n = gu.shape
     N = two_n // 2
     E = dense.shape[1] if dense is not None else 0
     out = torch.empty((T, N), dtype=out_dtype, device=gu.device)
     call("sllm_gated_clamp_act", _p(gu), _dt(gu), _p(dense), _p(out), _dtc(out_dtype), T, N, E, int(ff if dense is not None else N),
-         int(interleave), float(limit), float(alpha), _stream())
+         int(interleave), float(limit), float(alpha), {"clamped_swish": 0, "silu": 1}[act], _stream())
     return out
 
 
@@ -1489,6 +1538,41 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
     elif large:
         attention_mma(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, large, False, 1,
                       nq, nkv, hd, scale, window, out, block, sink)
+    return out
+
+
+def pool_kv_write(k_cache, v_cache, step, group: int, pk_cache, pv_cache, pool_group: int, pool: int) -> None:
+    """The tokens of the step that complete a block of ``pool`` positions write the means of the block's cached keys and of
+    its values (float32 sums in ascending order) into the pooled pages, at the places the step's description gives."""
+    _chk(k_cache, v_cache, pk_cache, pv_cache)
+    g, pg = step.groups[group], step.groups[pool_group]
+    num_pages, nkv, page_size, D = k_cache.shape
+    if tuple(pk_cache.shape[1:]) != (nkv, page_size, D) or pk_cache.dtype != k_cache.dtype:
+        raise KernelError("pool_kv_write: the pooled pages have the token pages' heads, page size and dtype")
+    call("sllm_pool_kv_write", _p(k_cache), _p(v_cache), _dt(k_cache), _p(g.block_tables), g.block_tables.shape[1], _p(step.positions),
+         _p(step.seq_of_token), _p(pg.slot_mapping), _p(pk_cache), _p(pv_cache), pk_cache.shape[0], step.num_tokens, nkv, D,
+         page_size, int(pool), _stream())
+
+
+def pooled_attention(q, k_cache, v_cache, pk_cache, pv_cache, step, group: int, pool_group, nq: int, nkv: int, vdim: int, scale: float,
+                     window, pool: int, sink=None, out_scale: float = 1.0, out=None, out_off: int = 0) -> torch.Tensor:
+    """Softmax attention of the step's queries ``q [T, nq*D]`` over the last ``window`` cached tokens and, beside them, over
+    the pooled entry of every block of ``pool`` positions that lies wholly before the window (``window`` None: all earlier
+    tokens, no entries).  ``sink`` (float32 ``[nq]``): exp(sink_h) joins the denominator.  The result, times ``out_scale``,
+    goes to columns ``out_off ..`` of ``out`` (made ``[T, nq*vdim]`` if not given), ``vdim`` value channels a head."""
+    _chk(q, k_cache, v_cache, pk_cache, pv_cache, sink, out)
+    g = step.groups[group]
+    T = q.shape[0]
+    num_pages, nkv_c, page_size, D = k_cache.shape
+    if nkv_c != nkv or q.shape[1] != nq * D or q.dtype != k_cache.dtype:
+        raise KernelError("pooled_attention: queries [T, nq*D] in the cache's dtype, a cache [pages, nkv, page_size, D]")
+    if out is None:
+        out = torch.empty((T, nq * vdim), dtype=q.dtype, device=q.device)
+    pg = step.groups[pool_group] if (pool_group is not None and window) else None
+    call("sllm_attention_pooled_simt", _p(q), _p(k_cache), _p(v_cache), _p(pk_cache) if pg else None, _p(pv_cache) if pg else None,
+         _dt(q), _p(g.block_tables), g.block_tables.shape[1], _p(pg.block_tables) if pg else None,
+         pg.block_tables.shape[1] if pg else 0, _p(step.positions), _p(step.seq_of_token), T, nq, nkv, D, int(vdim), page_size,
+         float(scale), int(window or 0), int(pool or 0), _p(sink), float(out_scale), _p(out), out.shape[1], int(out_off), _stream())
     return out
 
 

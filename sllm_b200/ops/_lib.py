@@ -50,12 +50,13 @@ def _declare(L):
         "sllm_delta_rule_supports": [c_int, c_int],
         "sllm_delta_rule": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_int, c_int, c_int, c_int, c_int, c_void_p],
-        "sllm_delta_out": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "sllm_delta_out": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                           c_int, c_void_p],
         "sllm_gated_delta_rule": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "sllm_gated_linear_attention": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
-        "sllm_qk_norm_rope_kv_write": [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+        "sllm_qk_norm_rope_kv_write": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                        c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                        c_void_p],
         "sllm_short_conv_silu": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -125,8 +126,17 @@ def _declare(L):
         "sllm_mingru_scan": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                              c_int, c_void_p],
         "sllm_gated_clamp_act": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
-                                 c_void_p],
-        "sllm_moe_route_top_softmax": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+                                 c_int, c_void_p],
+        "sllm_moe_route_top_softmax": [c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p],
+        "sllm_add_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "sllm_norm_pair": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "sllm_forget_gate_attention": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "sllm_pool_kv_write": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "sllm_attention_pooled_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
+                                       c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                       c_void_p, c_float, c_void_p, c_int, c_int, c_void_p],
         "sllm_rope_cols": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_void_p],
         "sllm_short_conv": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,

@@ -90,11 +90,17 @@ class PagedKV:
     """Keys and values per token, in pages.  ``window``: only the last
     ``window`` positions are ever read again (None: all).  ``values`` false: one vector
     per token serves as key and as value (a cached latent); the run's `LayerCache.v` is
-    then its ``k``, and nothing is stored twice."""
+    then its ``k``, and nothing is stored twice.  ``stride`` > 1: one entry per ``stride`` tokens (a summary of each
+    complete block of that many positions, written when the block's last token arrives), so a request of n tokens holds
+    n // stride entries and pages for those; such a cache has no window.  A layer may hold several paged caches under
+    different ``name`` s (its tokens' keys and the blocks' summaries); the first is `LayerCache.k` / ``.v``, every one
+    is found in `LayerCache.paged`."""
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     values: bool = True
+    stride: int = 1
+    name: str = "kv"
 
 
 @dataclass(frozen=True)
@@ -164,6 +170,7 @@ class LayerCache:
     v: torch.Tensor | None = None
     state: torch.Tensor | None = None   # [num_slots, *shape] float32 (the first of `states`)
     states: dict = field(default_factory=dict)   # name -> [num_slots, *shape] float32
+    paged: dict = field(default_factory=dict)    # name -> LayerCache(group, k, v) of every paged cache the run holds
 
 
 # ---- a norm whose division is still owed --------------------------------------------

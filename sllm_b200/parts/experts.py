@@ -81,7 +81,12 @@ class GatedExperts(FeedForward):
         expert e:  g = min(W_gate,e x, limit),  u = clamp(W_up,e x, -limit, limit),  W_down,e (g sigmoid(alpha g) (u + 1))
         out = sum over the winners of weight_e * expert_e(x)
 
-    Parameters: ``hidden_size``, ``experts``, ``top``, ``expert_ff``, ``limit``, ``alpha`` (1.702 unless given); no biases.  As
+    With ``activation`` = ``silu`` an expert is W_down,e (silu(W_gate,e x) * W_up,e x) instead (no limit); ``scale`` (1 unless
+    given) multiplies the weights.  The softmax over the winners alone is also what a softmax over ALL experts gives once
+    the winners' scores are divided by their sum.
+
+    Parameters: ``hidden_size``, ``experts``, ``top``, ``expert_ff``, ``limit``, ``alpha`` (1.702 unless given), ``activation``
+    (``clamped_swish`` unless given), ``scale``; no biases.  As
     in `RoutedExperts`, all experts' gate and up projections are ONE matrix (expert e's rows at 2 e ff, gate and up rows
     alternating in blocks of 8, or all of the expert's gate rows before its up rows where ff is no multiple of 8) and their
     down projections one matrix side by side; a token's activation row carries its routing weights, so the second product
@@ -93,7 +98,11 @@ class GatedExperts(FeedForward):
         self.hidden = int(p["hidden_size"])
         self.E, self.top = int(p["experts"]), int(p["top"])
         self.ff = int(p["expert_ff"])
-        self.limit, self.alpha = float(p["limit"]), float(p.get("alpha", 1.702))
+        self.act = str(p.get("activation", "clamped_swish"))
+        if self.act not in ("clamped_swish", "silu"):
+            raise ValueError(f"gated_experts: activation {self.act!r}; known: clamped_swish, silu")
+        self.limit, self.alpha = float(p.get("limit", 0.0) if self.act == "silu" else p["limit"]), float(p.get("alpha", 1.702))
+        self.scale = float(p.get("scale", 1.0))
         self.interleave = 8 if self.ff % 8 == 0 else self.ff
         if not 1 <= self.top <= self.E:
             raise ValueError(f"gated_experts: top={self.top} of {self.E} experts cannot be chosen")
@@ -120,12 +129,12 @@ class GatedExperts(FeedForward):
 
     def route(self, x):
         """(dense weights [T, E], indices [T, top], weights [T, top]) of the normed rows ``x``."""
-        return ops.moe_route_top_softmax(self.router(x, torch.float32), self.top)
+        return ops.moe_route_top_softmax(self.router(x, torch.float32), self.top, self.scale)
 
     def forward(self, x, step, residual=None):
         dense, _, _ = self.route(x)
         gu = self.gate_up(x, self.dtype)                                                                     # [T, 2 E ff]
-        act = ops.gated_clamp_act(gu, self.interleave, self.limit, self.dtype, alpha=self.alpha, dense=dense, ff=self.ff)
+        act = ops.gated_clamp_act(gu, self.interleave, self.limit, self.dtype, alpha=self.alpha, dense=dense, ff=self.ff, act=self.act)
         return self.down.into(act, residual)
 
     def weight_bytes(self):

@@ -139,3 +139,63 @@ class DecayLinearAttention(Mixer):
 
     def weight_bytes(self):
         return self.inp.nbytes() + self.out.nbytes() + 4 * self.gain.numel() + 4 * self.heads
+
+
+@MIXERS.register("forget_gate_attention")
+class ForgetGateAttention(Mixer):
+    """Linear attention whose forget gate also decides what is written (HGRN2):
+
+        S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T,        o_t = S_t^T q_t
+
+    with q = silu(W_q x) (heads x dim), v = W_v x (heads x vdim) and, per head and key channel,
+    f = lower + (1 - lower) sigmoid(W_f x + b): there is no key and no other scale.  Each head's o over its root mean
+    square times a gain of ``vdim`` numbers shared by the heads, then W_o.  Parameters: ``hidden_size``, ``heads``, ``dim``,
+    ``vdim``, ``eps`` (of the output's norm), ``out_scale`` (a factor on the mixer's term, 1 unless given; it rides on the
+    gain).  q, the gate's logits and v are one matrix whose product stays float32, as everything that enters the
+    recurrence does."""
+
+    NAMES = ("q", "f", "v")
+
+    def __init__(self, params, **kw):
+        super().__init__(params, **kw)
+        self.hidden = int(params["hidden_size"])
+        self.heads = int(params["heads"])
+        self.dim = int(params["dim"])
+        self.vdim = int(params["vdim"])
+        self.eps = float(params["eps"])
+        self.out_scale = float(params.get("out_scale", 1.0))
+        if not ops.delta_rule_supports(self.dim, self.vdim):
+            raise ValueError(f"forget_gate_attention: a head of {self.dim} key channels is outside what the recurrence kernel "
+                             f"keeps in registers (1..256)")
+
+    def cache_need(self):
+        return SlotState((self.heads, self.dim, self.vdim), "forget_gate")
+
+    def tensor_specs(self):
+        H, W = self.heads, self.hidden
+        K, V = H * self.dim, H * self.vdim
+        return [TensorSpec("q", (K, W)), TensorSpec("f", (K, W)), TensorSpec("f.b", (K,), role="bias"),
+                TensorSpec("lower", (K,), role="mix"), TensorSpec("v", (V, W)), TensorSpec("norm", (self.vdim,), role="gain"),
+                TensorSpec("o", (W, V))]
+
+    def bind(self, fetch):
+        K = self.heads * self.dim
+        self.inp = Linear(self._matrix(torch.cat([fetch(n) for n in self.NAMES], dim=0)))
+        self.offs = (0, K, 2 * K)
+        self.f_bias, self.lower = self._f32(fetch("f.b")), self._f32(fetch("lower"))
+        self.gain = self._f32(fetch("norm").float().repeat(self.heads) * self.out_scale)
+        self.out = Linear(self._matrix(fetch("o")))
+
+    accepts_residual = True
+
+    def mix(self, x, step: StepContext, cache: LayerCache, position=None, write_cache=True, out=None, out_off=0):
+        proj = self.inp(x, torch.float32)                                            # [T, 2K + V] float32
+        o = ops.forget_gate_attention(proj, self.offs, self.f_bias, self.lower, cache.states["forget_gate"], step, self.heads,
+                                      self.dim, self.vdim)                           # [T, V] float32
+        return ops.delta_out(o, self.gain, None, 0, self.eps, self.heads, self.vdim, self.dtype, "none", out=out, out_off=out_off)
+
+    def forward(self, x, step, cache, position, write_cache=True, residual=None):
+        return self.out.into(self.mix(x, step, cache, position, write_cache), residual)
+
+    def weight_bytes(self):
+        return self.inp.nbytes() + self.out.nbytes() + 4 * (self.gain.numel() + 2 * self.f_bias.numel())

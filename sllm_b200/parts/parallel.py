@@ -54,9 +54,11 @@ class GroupRMSNorm(Norm):
         if terms:
             ops.add_group_ssq(residual, terms, self.groups, self.eps, want_rinv=False)
 
-    def add_norm(self, residual, delta):
+    def add_norm(self, residual, delta, out_dtype=None):
+        """``out_dtype``: the normed copy's dtype where it is not the compute dtype (a norm whose output enters the float32
+        stream itself)."""
         self.complete(residual, delta)
-        return ops.group_norm_shift(residual, None, self.weight, self.dtype, groups=self.groups, eps=self.eps)
+        return ops.group_norm_shift(residual, None, self.weight, out_dtype or self.dtype, groups=self.groups, eps=self.eps)
 
     def weight_bytes(self):
         return self.size * 4
@@ -208,6 +210,54 @@ class ParallelShiftBlock:
         if len(terms) == 2 and not isinstance(next_norm, GroupRMSNorm):
             ops.add_group_ssq(residual, terms[:1], 1, 0.0, want_rinv=False)
             terms = terms[1:]
+        return terms[0] if len(terms) == 1 else tuple(terms)
+
+
+@BLOCKS.register("parallel_pair")
+class ParallelPairBlock:
+    """x <- x + (mixer(norm_a(x)) + ffn(norm_b(x))): two norms of the same x, one for each sublayer, both taken before
+    either term is added.  The norms are plain RMS norms (`group_rmsnorm` with one group) of one eps: one kernel takes the
+    row's root mean square once and writes both.  The feed-forward (with its norm) is optional.  Whatever factor the
+    design puts on the sum is the parts' business (they scale their own terms).  Roles: ``mixer_norm``, ``mixer``,
+    ``ffn_norm``, ``ffn``."""
+
+    ROLES = ("mixer_norm", "mixer", "ffn_norm", "ffn")
+
+    def __init__(self, parts: dict):
+        if set(parts) != set(self.ROLES) and set(parts) != {"mixer_norm", "mixer"}:
+            raise ValueError(f"the two-norm parallel block arranges {self.ROLES} (or mixer_norm and mixer alone); the layer names {sorted(parts)}")
+        self.mixer, self.ffn = parts["mixer"], parts.get("ffn")
+        self.mixer_norm, self.ffn_norm = parts["mixer_norm"], parts.get("ffn_norm")
+        for n in (self.mixer_norm, self.ffn_norm):
+            if n is not None and not (isinstance(n, GroupRMSNorm) and n.groups == 1):
+                raise ValueError("the two-norm parallel block's norms are group_rmsnorm with one group")
+        if self.ffn_norm is not None and self.ffn_norm.eps != self.mixer_norm.eps:
+            raise ValueError("the two-norm parallel block's norms share one eps")
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    accepts_next_norm = True
+
+    @property
+    def first_norm(self):
+        return self.mixer_norm
+
+    def forward(self, residual, delta, step, cache, position, write_cache=True, next_norm=None):
+        na, nb = self.mixer_norm, self.ffn_norm
+        na.complete(residual, delta)
+        ha, hb = ops.norm_pair(residual, na.weight, nb.weight if nb is not None else None, na.eps, na.dtype)
+        kw = {"residual": residual} if getattr(self.mixer, "accepts_residual", False) else {}
+        terms = [self.mixer.forward(ha, step, cache, position, write_cache, **kw)]
+        if self.ffn is not None:
+            kw = {"residual": residual} if getattr(self.ffn, "accepts_residual", False) else {}
+            terms.append(self.ffn.forward(hb, step, **kw))
+        terms = [t for t in terms if t is not None]
+        if len(terms) == 2 and not isinstance(next_norm, GroupRMSNorm):
+            ops.add_group_ssq(residual, terms[:1], 1, 0.0, want_rinv=False)
+            terms = terms[1:]
+        if not terms:
+            return None
         return terms[0] if len(terms) == 1 else tuple(terms)
 
 

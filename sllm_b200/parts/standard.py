@@ -92,7 +92,11 @@ class Rotary(PositionEncoding):
     ``original`` positions and leaves the fast ones alone: with c(t) = rot * ln(original / (2 pi t)) / (2 ln theta) the
     channel that turns t times over the original context, lo = max(floor(c(fast)), 0), hi = min(ceil(c(slow)), rot - 1)
     and ramp_j = clamp((j - lo) / max(hi - lo, 0.001), 0, 1), channel j's frequency becomes f_j / factor * ramp_j +
-    f_j * (1 - ramp_j), and cos and sin are multiplied by 0.1 ln(factor) + 1."""
+    f_j * (1 - ramp_j), and cos and sin are multiplied by 0.1 ln(factor) + 1.
+
+    A ``scaling`` with ``low`` and ``high`` in place of ``fast`` and ``slow`` goes by each channel's wavelength
+    l = 2 pi / f instead: f stays where l < original / high, becomes f / factor where l > original / low, and in between
+    is (1 - s) f / factor + s f with s = (original / l - low) / (high - low); cos and sin keep their size."""
 
     def __init__(self, params, **kw):
         super().__init__(params, **kw)
@@ -114,6 +118,12 @@ class Rotary(PositionEncoding):
         if not scaling:
             return f, 1.0
         factor, original = float(scaling["factor"]), float(scaling["original"])
+        if "low" in scaling:
+            low, high = float(scaling["low"]), float(scaling["high"])
+            wave = 2.0 * np.pi / f
+            s = (original / wave - low) / (high - low) if high != low else np.zeros_like(f)
+            blend = (1.0 - s) * f / factor + s * f
+            return np.where(wave < original / high, f, np.where(wave > original / low, f / factor, blend)), 1.0
 
         def channel(turns):
             return rot * np.log(original / (2.0 * np.pi * turns)) / (2.0 * np.log(theta))

@@ -96,13 +96,48 @@ def delta_rule(proj, offs, decay, a_bias, state, step, heads, dk, dv):
     return out.reshape(T, heads * dv)
 
 
-def delta_out(o, gain, proj, off_g, eps, heads, dv, out_dtype, gate_act="sigmoid"):
+def delta_out(o, gain, proj, off_g, eps, heads, dv, out_dtype, gate_act="sigmoid", out=None, out_off=0):
     T = o.shape[0]
     x = o.reshape(T, heads, dv)
     x = x * (x.pow(2).mean(-1, keepdim=True) + eps).rsqrt()
-    g = proj[:, off_g:off_g + heads * dv]
-    gate = torch.sigmoid(g) if gate_act == "sigmoid" else g * torch.sigmoid(g)
-    return (x.reshape(T, heads * dv) * gain * gate).to(out_dtype)
+    if gate_act == "none":
+        gate = 1.0
+    else:
+        g = proj[:, off_g:off_g + heads * dv]
+        gate = torch.sigmoid(g) if gate_act == "sigmoid" else g * torch.sigmoid(g)
+    y = x.reshape(T, heads * dv) * gain * gate
+    if out is None:
+        return y.to(out_dtype)
+    out[:, out_off:out_off + heads * dv] = y.to(out.dtype)
+    return out
+
+
+def forget_gate_attention(proj, offs, f_bias, lower, state, step, heads, dk, dv):
+    T = proj.shape[0]
+    off_q, off_f, off_v = offs
+    q = proj[:, off_q:off_q + heads * dk]
+    q = (q * torch.sigmoid(q)).reshape(T, heads, dk)
+    f = (lower + (1.0 - lower) * torch.sigmoid(proj[:, off_f:off_f + heads * dk] + f_bias)).reshape(T, heads, dk)
+    v = proj[:, off_v:off_v + heads * dv].reshape(T, heads, dv)
+    out = torch.empty((T, heads, dv), dtype=torch.float32, device=proj.device)
+
+    def token(t, S):
+        S = f[t][:, :, None] * S + (1.0 - f[t])[:, :, None] * v[t][:, None, :]
+        return S, torch.einsum("hij,hi->hj", S, q[t])
+    _walk(step, state, out, token)
+    return out.reshape(T, heads * dv)
+
+
+def add_rows_(stream, rows, vec):
+    if rows is not None:
+        stream += rows
+    if vec is not None:
+        stream += vec
+
+
+def norm_pair(stream, gain_a, gain_b, eps, out_dtype):
+    x = stream * (stream.pow(2).mean(-1, keepdim=True) + eps).rsqrt()
+    return (x * gain_a).to(out_dtype), ((x * gain_b).to(out_dtype) if gain_b is not None else None)
 
 
 def _walk(step, state, out, token):
@@ -155,13 +190,16 @@ def gated_linear_attention(proj, offs, z, state, step, heads, dk, dv, q_scale, t
 
 
 def qk_norm_rope_kv_write(qkv, q_gain, k_gain, eps, positions, table, rotary_dim, nq, nkv, dim, vdim, slot_mapping, k_cache, v_cache,
-                          out_dtype):
+                          out_dtype, q_mul=None):
     T = qkv.shape[0]
     D = k_cache.shape[3]
     qk = qkv[:, :(nq + nkv) * dim].float().reshape(T, nq + nkv, dim)
     v = qkv[:, (nq + nkv) * dim:(nq + nkv) * dim + nkv * vdim].float().reshape(T, nkv, vdim)
-    qk = qk * (qk.pow(2).mean(-1, keepdim=True) + eps).rsqrt()
-    qk = torch.cat([qk[:, :nq] * q_gain, qk[:, nq:] * k_gain], dim=1)
+    if q_gain is not None:
+        qk = qk * (qk.pow(2).mean(-1, keepdim=True) + eps).rsqrt()
+        qk = torch.cat([qk[:, :nq] * q_gain, qk[:, nq:] * k_gain], dim=1)
+    if q_mul is not None:
+        qk = torch.cat([qk[:, :nq] * q_mul[None, :, None], qk[:, nq:]], dim=1)
     if rotary_dim:
         half = rotary_dim // 2
         cs = table[positions.long()]
@@ -308,22 +346,26 @@ def short_conv_add(x, weight, state, step, out_dtype):
     return out.to(out_dtype)
 
 
-def moe_route_top_softmax(logits, top):
+def moe_route_top_softmax(logits, top, scale=1.0):
     T, E = logits.shape
     idx = torch.sort(-logits.float(), dim=-1, stable=True).indices[:, :top]
-    wts = torch.softmax(logits.float().gather(1, idx), dim=-1)
+    wts = torch.softmax(logits.float().gather(1, idx), dim=-1) * scale
     dense = torch.zeros((T, E), dtype=torch.float32, device=logits.device)
     dense.scatter_(1, idx, wts)
     return dense, idx.int(), wts
 
 
-def gated_clamp_act(gu, interleave, limit, out_dtype, *, alpha=1.702, dense=None, ff=None):
+def gated_clamp_act(gu, interleave, limit, out_dtype, *, alpha=1.702, dense=None, ff=None, act="clamped_swish"):
     T, two_n = gu.shape
     N = two_n // 2
     v = gu.float().reshape(T, N // interleave, 2, interleave)
-    g = v[:, :, 0, :].reshape(T, N).clamp(max=limit)
-    u = v[:, :, 1, :].reshape(T, N).clamp(-limit, limit)
-    y = g * torch.sigmoid(alpha * g) * (u + 1.0)
+    if act == "silu":
+        g, u = v[:, :, 0, :].reshape(T, N), v[:, :, 1, :].reshape(T, N)
+        y = g * torch.sigmoid(g) * u
+    else:
+        g = v[:, :, 0, :].reshape(T, N).clamp(max=limit)
+        u = v[:, :, 1, :].reshape(T, N).clamp(-limit, limit)
+        y = g * torch.sigmoid(alpha * g) * (u + 1.0)
     if dense is not None:
         y = y * dense.repeat_interleave(ff, dim=1)
     return y.to(out_dtype)
@@ -469,6 +511,55 @@ def paged_attention(q, k_cache, v_cache, step, group, nq, nkv, hd, scale, window
                           nq, nkv, hd, scale, window, block, sink)
 
 
+def pool_kv_write(k_cache, v_cache, step, group, pk_cache, pv_cache, pool_group, pool):
+    g, pg = step.groups[group], step.groups[pool_group]
+    ps = k_cache.shape[2]
+    for t in range(step.num_tokens):
+        slot = int(pg.slot_mapping[t])
+        if slot < 0:
+            continue
+        pos = int(step.positions[t])
+        j = torch.arange(pos - pool + 1, pos + 1, device=k_cache.device)
+        pages = g.block_tables[int(step.seq_of_token[t])].long()[j // ps]
+        pk_cache[slot // ps, :, slot % ps, :] = k_cache[pages, :, j % ps, :].float().mean(0).to(pk_cache.dtype)
+        pv_cache[slot // ps, :, slot % ps, :] = v_cache[pages, :, j % ps, :].float().mean(0).to(pv_cache.dtype)
+
+
+def pooled_attention(q, k_cache, v_cache, pk_cache, pv_cache, step, group, pool_group, nq, nkv, vdim, scale, window, pool, sink=None,
+                     out_scale=1.0, out=None, out_off=0):
+    g = step.groups[group]
+    pg = step.groups[pool_group] if (pool_group is not None and window) else None
+    T = q.shape[0]
+    ps, D = k_cache.shape[2], k_cache.shape[3]
+    res = torch.empty((T, nq, vdim), dtype=torch.float32, device=q.device)
+    qf = q.float().reshape(T, nq, D)
+    rep = nq // nkv
+    for t in range(T):
+        pos, seq = int(step.positions[t]), int(step.seq_of_token[t])
+        lo = max(0, pos - window + 1) if window else 0
+        j = torch.arange(lo, pos + 1, device=q.device)
+        pages = g.block_tables[seq].long()[j // ps]
+        k, v = k_cache[pages, :, j % ps, :].float(), v_cache[pages, :, j % ps, :].float()
+        nb = lo // pool if pg is not None else 0
+        if nb:
+            b = torch.arange(nb, device=q.device)
+            bp = pg.block_tables[seq].long()[b // ps]
+            k = torch.cat([pk_cache[bp, :, b % ps, :].float(), k], dim=0)
+            v = torch.cat([pv_cache[bp, :, b % ps, :].float(), v], dim=0)
+        k, v = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)[..., :vdim]
+        s = torch.einsum("hd,nhd->hn", qf[t], k) * scale
+        if sink is not None:
+            p = torch.softmax(torch.cat([s, sink.float()[:, None]], dim=-1), dim=-1)[:, :-1]
+        else:
+            p = torch.softmax(s, dim=-1)
+        res[t] = torch.einsum("hn,nhd->hd", p, v) * out_scale
+    res = res.reshape(T, nq * vdim)
+    if out is None:
+        return res.to(q.dtype)
+    out[:, out_off:out_off + nq * vdim] = res.to(out.dtype)
+    return out
+
+
 def gather_rows(x, rows):
     if x.dim() == 3:
         return x[:, rows.long()].sum(0)
@@ -515,7 +606,7 @@ def penalty_from_seen_(logits, seen, step, penalty):
     return logits
 
 
-ALL = ["post_add_norm_conv", "latent_rope_write", "rope_cols_", "short_conv_add", "moe_route_top_softmax", "gated_clamp_act", "post_add_norm", "mingru_scan",
+ALL = ["forget_gate_attention", "add_rows_", "norm_pair", "pool_kv_write", "pooled_attention", "post_add_norm_conv", "latent_rope_write", "rope_cols_", "short_conv_add", "moe_route_top_softmax", "gated_clamp_act", "post_add_norm", "mingru_scan",
        "decay_linear_attention", "gated_delta_rule", "gated_linear_attention", "qk_norm_rope_kv_write", "short_conv_silu", "norm_mean_add_", "moe_route", "moe_act",
        "add_sinusoid_", "add_group_ssq", "group_norm_shift", "act_mul", "linear_act_mul", "tanh_cols", "delta_rule", "delta_out", "latent_write",
        "head_linear", "embed_gather", "add_rmsnorm", "linear", "can_accumulate", "linear_accumulate", "silu_mul", "linear_silu_mul", "rope_kv_write",
