@@ -113,7 +113,7 @@ def pooled_window_attention(q, k, v, scale, temp, window: int, pool: int):
     T, H, _ = q.shape
     G = k.shape[1]
     out = np.zeros((T, H, v.shape[2]), dtype=q.dtype)
-    nblocks = T // pool
+    nblocks = T // pool if pool else 0
     pk = np.stack([k[b * pool:(b + 1) * pool].mean(0) for b in range(nblocks)]) if nblocks else np.zeros((0,) + k.shape[1:], q.dtype)
     pv = np.stack([v[b * pool:(b + 1) * pool].mean(0) for b in range(nblocks)]) if nblocks else np.zeros((0,) + v.shape[1:], q.dtype)
     for i in range(T):
@@ -143,7 +143,10 @@ def attention_side(h, w, p, cfg, positions=None):
         f = rotary_frequencies(rot["base"], rot["dims"], rot.get("scaling"))
         pos = np.arange(T) if positions is None else positions
         q, k = rotate(q, pos, f), rotate(k, pos, f)
-    o = pooled_window_attention(q, k, v, p["scale"], w["temp"], p["mask"]["size"], p["mask"]["pool"])
+    mask = p.get("mask")
+    window = mask["size"] if mask else T + 1                      # no mask: every earlier token, no blocks
+    pool = mask.get("pool") if mask else None
+    o = pooled_window_attention(q, k, v, p["scale"], w["temp"], window, pool)
     return o.reshape(T, H * vdim) @ w["o"].T
 
 
@@ -185,10 +188,17 @@ def route(z, top: int, scale: float):
     return idx, chosen / (chosen.sum(-1, keepdims=True) + 1e-20) * scale
 
 
-def experts(h, w, p):
-    """The mixture: w by names under the feed-forward's prefix (``router``, ``e<i>.gate``, ``.up``, ``.down``)."""
+def experts(h, w, p, margins=None):
+    """The mixture: w by names under the feed-forward's prefix (``router``, ``e<i>.gate``, ``.up``, ``.down``).  ``margins``
+    (a list) receives, per token, the gap between the last chosen logit and the best one left out, relative to the
+    logits' size (infinite where every expert is chosen)."""
     r = p["router"]
-    idx, wts = route(h @ w["router"].T, r["top"], r["scale"])
+    z = h @ w["router"].T
+    idx, wts = route(z, r["top"], r["scale"])
+    if margins is not None:
+        zs = -np.sort(-z, axis=-1)
+        top = r["top"]
+        margins.append((zs[:, top - 1] - zs[:, top]) / (np.abs(z).max(-1) + 1e-30) if top < z.shape[1] else np.full(len(z), np.inf))
     out = np.zeros((h.shape[0], w["e0.down"].shape[0]), dtype=h.dtype)
     for t in range(h.shape[0]):
         for e, a in zip(idx[t], wts[t]):
@@ -216,7 +226,7 @@ def run_order(cfg):
     return order
 
 
-def layer(x, i, cfg, weights):
+def layer(x, i, cfg, weights, margins=None):
     lc = cfg["layers"][i]
     eps, m = cfg["norm"]["eps"], cfg["residual_mult"]
     mix = lc["mixer"]
@@ -225,12 +235,13 @@ def layer(x, i, cfg, weights):
         + mix["right_scale"] * recurrent_side(h1, sub(weights, f"l{i}.mix.right"), mix["right"], eps)
     if lc.get("mlp") is not None:
         h2 = rms_norm(x, weights[f"l{i}.norm2"], eps)
-        term = term + experts(h2, sub(weights, f"l{i}.mlp"), lc["mlp"])
+        term = term + experts(h2, sub(weights, f"l{i}.mlp"), lc["mlp"], margins)
     return x + m * term
 
 
-def forward(cfg, weights, tokens, collect=None):
-    """Logits [T, vocab] of one sequence.  ``collect``: a list that receives the stream after every layer run."""
+def forward(cfg, weights, tokens, collect=None, margins=None):
+    """Logits [T, vocab] of one sequence.  ``collect``: a list that receives the stream after every layer run; ``margins``:
+    one that receives every router's margins (see `experts`)."""
     eps = cfg["norm"]["eps"]
     emb = rms_norm(weights["embed"][np.asarray(tokens)], weights["embed.norm"], eps)
     x = emb.copy()
@@ -240,7 +251,7 @@ def forward(cfg, weights, tokens, collect=None):
             if t > 0:
                 x = x + emb
             x = x + weights["loop.step"][t]
-        x = layer(x, i, cfg, weights)
+        x = layer(x, i, cfg, weights, margins)
         if collect is not None:
             collect.append(x.copy())
     return rms_norm(x, weights["final.norm"], eps) @ weights["embed"].T
