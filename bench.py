@@ -215,7 +215,7 @@ def decode_run(model, cfg, batch, context, steps, warmup, seed=0, graphs=True, r
     # bytes the step has to read: every weight once, and the live requests' cache (the median region's contexts)
     mid = sorted(range(repeats), key=lambda r: dev[r])[repeats // 2]
     ctx_mean = prompt_len + warmup + mid * steps + (steps - 1) / 2.0
-    kv_bytes = llm.engine.cache.bytes_per_token(2 if model.dtype == torch.bfloat16 else 4) * ctx_mean * batch
+    kv_bytes = llm.engine.cache.bytes_read(2 if model.dtype == torch.bfloat16 else 4, ctx_mean) * batch
     # (a recurrent layer's state is read and written once a step and request; none in an attention-only model)
     step_bytes = model.weight_bytes() + kv_bytes + 2 * llm.engine.cache.state_bytes_per_request() * batch
     # per step: the packed batch description (one pinned buffer: ids, positions, slots, block tables, sampling
@@ -455,6 +455,24 @@ def kidolorn_config(sz: dict) -> dict:
     return {"architecture": "Kidolorn", "vocab": sz["vocab"], "width": W, "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "layers": layers}
 
 
+def gerupel_config(sz: dict) -> dict:
+    """Gerupel at one size: the same width, vocabulary and number of layer runs (two of its layers fewer, the two in the
+    middle run twice); every layer holds grouped-query attention (an eighth of the heads as kv heads, half the head rotated
+    with a frequency scaling) over a window of 1,024 tokens plus one pooled key and value per block of 64 older tokens,
+    beside a forget-gate linear attention with heads of 128 x 128 (the state of Nutopel's gated delta heads), and
+    Nutopel's mixture without its shared expert: eight experts of a quarter of the dense size, two of them used."""
+    W, H, D = sz["width"], sz["heads"], sz["dim"]
+    mlp = {"kind": "moe", "expert": {"ff": sz["ff"] // 4 // 64 * 64}, "router": {"experts": 8, "top": 2, "scale": 2.0}}
+    left = {"heads": H, "kv_heads": max(1, H // 8), "dim": D, "vdim": D, "mask": {"size": 1024, "pool": 64}, "scale": D ** -0.5,
+            "rot": {"base": 10000.0, "dims": D // 2, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 2048}}}
+    right = {"heads": W // 128, "dim": 128, "vdim": 128}
+    layer = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}, "mlp": mlp}
+    n = max(sz["layers"] - 2, 2)
+    return {"architecture": "Gerupel", "vocab": sz["vocab"], "width": W, "residual_mult": 0.5, "norm": {"eps": 1e-5},
+            "loop": {"start": n // 2 - 1, "stop": n // 2 + 1, "times": 2} if sz["layers"] >= 4 else None,
+            "layers": [layer for _ in range(n if sz["layers"] >= 4 else sz["layers"])]}
+
+
 def design_run(args) -> dict:
     global PREFILL_TOKENS
     import torch
@@ -472,6 +490,9 @@ def design_run(args) -> dict:
         if args.workload == "kidolorn":
             designs.insert(0, ("kidolorn", kidolorn_config(sz)))
             designs = designs[:3]                   # beside Nutopel (experts, linear attention) and Rososun (latent attention)
+        if args.workload == "gerupel":
+            # beside Nutopel (attention next to a matrix-state recurrence, experts) and Qwen2 (grouped-query attention)
+            designs = [("gerupel", gerupel_config(sz)), ("nutopel", nutopel_config(sz)), designs[-1]]
         for which, config in designs:
             model, _ = build_random_model(config, seed=0, dtype="bfloat16", device="cuda:0", std=0.02)
             cfg = {"vocab_size": sz["vocab"]}
@@ -746,7 +767,7 @@ def base_config(cfg, args, prompt_len) -> dict:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", choices=("decode", "rososun", "nutopel", "kidolorn") + tuple(SERVING), default="decode",
+    ap.add_argument("--workload", choices=("decode", "rososun", "nutopel", "kidolorn", "gerupel") + tuple(SERVING), default="decode",
                     help="decode: the default run; serve-*: the baseline's serving workloads through LLM.generate")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)
@@ -785,7 +806,7 @@ def main(argv=None) -> int:
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device"}))
         return 1
-    if args.workload in ("rososun", "nutopel", "kidolorn"):
+    if args.workload in ("rososun", "nutopel", "kidolorn", "gerupel"):
         print(json.dumps(design_run(args)))
         return 0
     if args.workload != "decode":

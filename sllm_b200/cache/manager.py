@@ -262,6 +262,15 @@ class CacheManager:
         return sum(-(-len(g.runs) * (2 if g.need.values else 1) * g.need.num_kv_heads * g.need.head_dim * itemsize // g.need.stride)
                    for g in self.groups)
 
+    def bytes_read(self, itemsize: int, context: float) -> float:
+        """Bytes of cached keys and values a decoded token at ``context`` tokens reads: per group, the tokens its window
+        still shows (all of them without one), an entry per ``stride`` tokens where the group holds such."""
+        total = 0.0
+        for g in self.groups:
+            n = context if g.need.window is None else min(context, g.need.window)
+            total += len(g.runs) * (2 if g.need.values else 1) * g.need.num_kv_heads * g.need.head_dim * itemsize * (n / g.need.stride)
+        return total
+
     def state_bytes_per_request(self) -> int:
         """Bytes of fixed-size float32 state each request holds in the mixers' slots (tables that others
         register with `register_slot_table` are theirs to count)."""

@@ -13,6 +13,9 @@
 //                 end; the grid's z dimension splits the context further (split-KV), the
 //                 partial results go to scratch and a second kernel combines them.
 //
+// With pooled blocks (see `AttnParams`) a CTA first walks tiles of the blocks' entries that its rows may see, then the
+// window's token tiles; every row masks the entries and tokens that are not its own to see.
+//
 // Scores, softmax and the output accumulation are float32 (mma.sync m16n8k16, bf16 in,
 // f32 out); probabilities are rounded to bfloat16 for the P.V product.
 // Formulas: ref/qwen3_5.py:373-390 (scores * scale, causal mask, softmax, P.V);
@@ -42,6 +45,16 @@ struct AttnParams {
   int block;     // > 0: a query sees only keys of its own block of this many positions (counted from 0)
   float scale_log2;              // scale * log2(e)
   const float* sink;             // [nq] or null: exp(sink_h) joins the softmax's denominator (no key, no value, not scaled)
+  // pooled blocks beside a window (pool > 0; needs window > 0 and num_splits == 1): a query at position i also sees entry b
+  // of the pooled cache (same page geometry) for every b < (i - window + 1) / pool; these entries are walked as key tiles
+  // of their own before the window's
+  const __nv_bfloat16* pk_cache;
+  const __nv_bfloat16* pv_cache;
+  const int* pool_tables;        // [S, pool_max_pages]
+  int pool_max_pages, pool;
+  // out_ld > 0: the output row of token t and head h is out + t * out_ld + out_off + h * vdim, vdim <= HD channels of it
+  int out_ld, out_off, vdim;
+  float out_scale;               // a factor on the result
 };
 
 constexpr int ATT_BN = 64;     // keys per tile
@@ -94,12 +107,21 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
     key_hi = min(key_hi, (split + 1) * chunk);
   }
   const int tile0 = key_lo / ATT_BN * ATT_BN;    // tiles start at multiples of 64 keys, whatever the cut
-  const int n_tiles = key_hi > tile0 ? (key_hi - tile0 + ATT_BN - 1) / ATT_BN : 0;
+  const int n_tok_tiles = key_hi > tile0 ? (key_hi - tile0 + ATT_BN - 1) / ATT_BN : 0;
+  // pooled entries: as many as the tile's last row sees (earlier rows mask the rest)
+  int nb_max = 0;
+  if (p.pool > 0 && row_hi > row0) {
+    const int lo_last = pos0 + (row_hi - 1) / G - p.window + 1;
+    nb_max = lo_last > 0 ? lo_last / p.pool : 0;
+  }
+  const int n_ptiles = (nb_max + ATT_BN - 1) / ATT_BN;
+  const int n_tiles = n_ptiles + n_tok_tiles;
+  const int* pt = p.pool > 0 ? p.pool_tables + (size_t)seq * p.pool_max_pages : nullptr;
 
   // the pages of this CTA's key range, fetched once: a tile's loads then depend on shared
   // memory only, not on a global load of the table
   const int page_first = tile0 / p.page_size;
-  const int page_count = n_tiles > 0 ? (key_hi - 1) / p.page_size - page_first + 1 : 0;
+  const int page_count = n_tok_tiles > 0 ? (key_hi - 1) / p.page_size - page_first + 1 : 0;
   const bool bt_cached = page_count <= BT_CACHE;
   if (bt_cached) {
     for (int i = tid; i < page_count; i += NTHREADS) bt_s[i] = bt[page_first + i];
@@ -126,7 +148,26 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
   const size_t head_off = (size_t)kvh * ps * HD + ch8;
   const size_t page_stride = (size_t)p.nkv * ps * HD;
   auto load_kv = [&](int tile, int buf) {
-    const int kbase = tile0 + tile * ATT_BN;
+    if (tile < n_ptiles) {                        // a tile of pooled entries
+#pragma unroll
+      for (int r = r_first; r < ATT_BN; r += R_STEP) {
+        const int e = tile * ATT_BN + r;
+        bool ok = e < nb_max;
+        int page = 0, off = 0;
+        if (ok) {
+          const int pi = ps_shift >= 0 ? e >> ps_shift : e / ps;
+          off = e - pi * ps;
+          page = pi < p.pool_max_pages ? pt[pi] : -1;
+          ok = page >= 0;
+          if (!ok) page = 0;
+        }
+        const size_t src = (size_t)page * page_stride + head_off + (size_t)off * HD;
+        cp_async_16(k_s + (buf * ATT_BN + r) * STRIDE + ch8, p.pk_cache + src, ok);
+        cp_async_16(v_s + (buf * ATT_BN + r) * STRIDE + ch8, p.pv_cache + src, ok);
+      }
+      return;
+    }
+    const int kbase = tile0 + (tile - n_ptiles) * ATT_BN;
 #pragma unroll
     for (int r = r_first; r < ATT_BN; r += R_STEP) {
       const int key = kbase + r;
@@ -155,12 +196,14 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
 
   // ---- per-thread rows: g and g+8 of the warp's 16-row block ---------------------------
   const int wrow = DECODE ? 0 : warp * 16;
-  int hi_r[2], lo_r[2];
+  int hi_r[2], lo_r[2], nb_r[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int row = row0 + wrow + g + 8 * i;
+    nb_r[i] = 0;
     if (row < rows_total) {
       const int pos = pos0 + row / G;
+      if (p.pool > 0 && pos - p.window + 1 > 0) nb_r[i] = (pos - p.window + 1) / p.pool;
       hi_r[i] = min(pos + 1, key_hi);
       lo_r[i] = p.window > 0 ? max(key_lo, pos - p.window + 1) : key_lo;
       if (p.block > 0) lo_r[i] = max(lo_r[i], pos / p.block * p.block);
@@ -209,7 +252,8 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
       }
     }
     // mask, scale (into the log2 domain), row maxima
-    const int kbase = tile0 + tile * ATT_BN + koff;
+    const bool pooled_tile = tile < n_ptiles;
+    const int kbase = (pooled_tile ? tile * ATT_BN : tile0 + (tile - n_ptiles) * ATT_BN) + koff;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int n = 0; n < NT; ++n)
@@ -217,7 +261,8 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
       for (int c = 0; c < 4; ++c) {
         const int key = kbase + n * 8 + 2 * t4 + (c & 1);
         const int i = c >> 1;
-        const float v = (key < hi_r[i] && key >= lo_r[i]) ? s[n][c] * p.scale_log2 : -INFINITY;
+        const bool seen = pooled_tile ? key < nb_r[i] : (key < hi_r[i] && key >= lo_r[i]);
+        const float v = seen ? s[n][c] * p.scale_log2 : -INFINITY;
         s[n][c] = v;
         mx[i] = fmaxf(mx[i], v);
       }
@@ -278,8 +323,14 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
       if (row >= rows_total) continue;
       const size_t orow = (size_t)(q0 + row / G) * p.nq + kvh * G + row % G;
       if (p.sink != nullptr && p.num_splits == 1) l_r[i] += exp2f(p.sink[kvh * G + row % G] * 1.4426950408889634f - m_r[i]);
-      const float inv = l_r[i] > 0.f ? 1.f / l_r[i] : 0.f;
-      if (p.num_splits > 1) {
+      const float inv = l_r[i] > 0.f ? p.out_scale / l_r[i] : 0.f;
+      if (p.out_ld > 0) {
+        __nv_bfloat16* po = p.out + (size_t)(q0 + row / G) * p.out_ld + p.out_off + (size_t)(kvh * G + row % G) * p.vdim;
+#pragma unroll
+        for (int d = 0; d < DT; ++d)
+          if (d * 8 + 2 * t4 < p.vdim)
+            *reinterpret_cast<unsigned*>(po + d * 8 + 2 * t4) = pack_bf16(o[d][2 * i] * inv, o[d][2 * i + 1] * inv);
+      } else if (p.num_splits > 1) {
         float* po = p.part_o + ((size_t)split * p.total_tokens * p.nq + orow) * HD;
 #pragma unroll
         for (int d = 0; d < DT; ++d)
@@ -331,9 +382,14 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
         acc.x += v.x * f[w]; acc.y += v.y * f[w]; acc.z += v.z * f[w]; acc.w += v.w * f[w];
       }
       if (p.sink != nullptr && p.num_splits == 1) lt += exp2f(p.sink[kvh * G + row % G] * 1.4426950408889634f - mt);
-      const float inv = lt > 0.f ? 1.f / lt : 0.f;
+      const float inv = lt > 0.f ? p.out_scale / lt : 0.f;
       const size_t orow = (size_t)(q0 + row / G) * p.nq + kvh * G + row % G;
-      if (p.num_splits > 1) {
+      if (p.out_ld > 0) {
+        if (d4 < p.vdim) {
+          __nv_bfloat16* po = p.out + (size_t)(q0 + row / G) * p.out_ld + p.out_off + (size_t)(kvh * G + row % G) * p.vdim + d4;
+          *reinterpret_cast<uint2*>(po) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
+        }
+      } else if (p.num_splits > 1) {
         float* po = p.part_o + ((size_t)split * p.total_tokens * p.nq + orow) * HD + d4;
         *reinterpret_cast<float4*>(po) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
         if (d4 == 0) p.part_lse[(size_t)split * p.total_tokens * p.nq + orow] = lt > 0.f ? mt + log2f(lt) : -INFINITY;
@@ -436,6 +492,47 @@ SLLM_EXPORT int sllm_attention_mma(const void* q, const void* k_cache, const voi
   p.num_splits = num_splits; p.total_tokens = total_tokens;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.sink = sink;
+  p.pk_cache = p.pv_cache = nullptr; p.pool_tables = nullptr; p.pool_max_pages = p.pool = 0;
+  p.out_ld = p.out_off = p.vdim = 0; p.out_scale = 1.f;
+#define DISPATCH(HD_)                                                             \
+  case HD_:                                                                       \
+    return decode ? launch_attention<HD_, true>(p, tiles, stream) : launch_attention<HD_, false>(p, tiles, stream);
+  switch (hd) {
+    DISPATCH(16) DISPATCH(32) DISPATCH(64) DISPATCH(128)
+  }
+#undef DISPATCH
+  return SLLM_ERR_UNSUPPORTED;
+}
+
+// The same kernels over a window of tokens plus pooled blocks (see `AttnParams`): no split of the context; the result,
+// times `out_scale`, goes to columns out_off + h * vdim of rows of `out_ld` elements.
+SLLM_EXPORT int sllm_attention_mma_pooled(const void* q, const void* k_cache, const void* v_cache, const void* pk_cache,
+                                          const void* pv_cache, void* out, const int* block_tables, int max_pages,
+                                          const int* pool_tables, int pool_max_pages, const int* q_start, const int* ctx_len,
+                                          const int* tile_seq, const int* tile_row0, int tiles, int decode, int total_tokens,
+                                          int nq, int nkv, int hd, int vdim, int page_size, float scale, int window, int pool,
+                                          const float* sink, float out_scale, int out_ld, int out_off, cudaStream_t stream) {
+  SLLM_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_mma_pooled: bad head counts nq=%d nkv=%d", nq, nkv);
+  SLLM_REQUIRE(sllm_attention_mma_supports(hd), "attention_mma_pooled: head_dim=%d is not one of 16, 32, 64, 128", hd);
+  SLLM_REQUIRE(page_size > 0 && max_pages > 0 && tiles >= 0 && total_tokens >= 0 && nkv <= 65535, "attention_mma_pooled: bad sizes");
+  if (pool_max_pages <= 0) pool = 0;              // no request of the step holds an entry yet
+  SLLM_REQUIRE(pool == 0 || (window > 0 && pool_tables && pk_cache && pv_cache),
+               "attention_mma_pooled: pooled entries need a window, their pages and their tables");
+  SLLM_REQUIRE(vdim > 0 && vdim <= hd && vdim % 4 == 0 && out_ld % 4 == 0 && out_off % 4 == 0 && out_off >= 0 &&
+                   out_off + nq * vdim <= out_ld && ((uintptr_t)out & 7) == 0,
+               "attention_mma_pooled: the output's columns (%d heads of %d from %d in rows of %d) must be multiples of 4", nq, vdim, out_off, out_ld);
+  if (tiles == 0) return SLLM_OK;
+  AttnParams p;
+  p.q = (const __nv_bfloat16*)q; p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
+  p.out = (__nv_bfloat16*)out; p.part_o = nullptr; p.part_lse = nullptr; p.block_tables = block_tables;
+  p.q_start = q_start; p.ctx_len = ctx_len; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
+  p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.window = window; p.block = 0;
+  p.num_splits = 1; p.total_tokens = total_tokens;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.sink = sink;
+  p.pk_cache = (const __nv_bfloat16*)pk_cache; p.pv_cache = (const __nv_bfloat16*)pv_cache; p.pool_tables = pool_tables;
+  p.pool_max_pages = pool_max_pages; p.pool = pool;
+  p.out_ld = out_ld; p.out_off = out_off; p.vdim = vdim; p.out_scale = out_scale;
 #define DISPATCH(HD_)                                                             \
   case HD_:                                                                       \
     return decode ? launch_attention<HD_, true>(p, tiles, stream) : launch_attention<HD_, false>(p, tiles, stream);

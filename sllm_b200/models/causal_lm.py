@@ -102,8 +102,16 @@ class CausalLM:
         more when it is the embedding table: the step reads it whole as the head
         and only single rows of it as the embedding)."""
         n = self.head.numel() * self.head.element_size()
-        for _, part in self._named_parts():
-            n += part.weight_bytes()
+        runs = {}
+        for e in self.plan.run_list:            # a layer that runs several times in a step is read as often
+            runs[e.layer] = runs.get(e.layer, 0) + 1
+        for i, layer in enumerate(self.layers):
+            n += runs.get(i, 0) * sum(part.weight_bytes() for _, part in layer.named_parts())
+        n += self.final_norm.weight_bytes()
+        if self.embedding_norm is not None:
+            n += self.embedding_norm.weight_bytes()
+        if self.position is not None and self.plan.position_name:
+            n += self.position.weight_bytes()
         return n
 
     # ---- cache needs ----------------------------------------------------------------

@@ -305,12 +305,13 @@ def gated_linear_attention(proj, offs, z, state, step, heads: int, dk: int, dv: 
 # ---- two mixers side by side: normed, rotated attention heads; short convolutions; the normed mean ---------------
 
 def qk_norm_rope_kv_write(qkv, q_gain, k_gain, eps: float, positions, table, rotary_dim: int, nq: int, nkv: int, dim: int,
-                          vdim: int, slot_mapping, k_cache, v_cache, out_dtype, q_mul=None) -> torch.Tensor:
+                          vdim: int, slot_mapping, k_cache, v_cache, out_dtype, q_mul=None, col_off: int = 0) -> torch.Tensor:
     """From a float32 product ``[T, (nq+nkv)*dim + nkv*vdim]``: every query and key head over its root mean square times
     its gain (``[dim]``, shared by the heads), then rotated; values as they are.  The queries come back ``[T, nq*D]`` in
     ``out_dtype`` with D the cache's head size (>= dim and vdim; zeros beyond); keys and values go to ``slot_mapping`` in
     the pages (not written when ``slot_mapping`` is None).  With both gains None the heads are not normed; ``q_mul``
-    (float32 ``[nq]``) multiplies each query head."""
+    (float32 ``[nq]``) multiplies each query head.  ``col_off``: the column of ``qkv`` at which q|k|v start (a product that
+    holds other projections too)."""
     _chk(qkv, q_gain, k_gain, q_mul, positions, table, slot_mapping, k_cache, v_cache)
     T, ld = qkv.shape
     num_pages, nkv_c, page_size, D = k_cache.shape
@@ -322,7 +323,9 @@ def qk_norm_rope_kv_write(qkv, q_gain, k_gain, eps: float, positions, table, rot
             raise KernelError("qk_norm_rope_kv_write: rotary table must be float32 [positions, 2, rotary_dim/2]")
         max_pos = table.shape[0]
     q = torch.empty((T, nq * D), dtype=out_dtype, device=qkv.device)
-    call("sllm_qk_norm_rope_kv_write", _p(qkv), ld, _p(q_gain), _p(k_gain), _p(q_mul), float(eps), _p(positions), _p(table), int(rotary_dim),
+    if col_off < 0 or col_off + (nq + nkv) * dim + nkv * vdim > ld:
+        raise KernelError("qk_norm_rope_kv_write: q|k|v lie outside the product's columns")
+    call("sllm_qk_norm_rope_kv_write", _p(qkv) + 4 * int(col_off), ld, _p(q_gain), _p(k_gain), _p(q_mul), float(eps), _p(positions), _p(table), int(rotary_dim),
          max_pos, nq, nkv, dim, vdim, D, _p(slot_mapping), page_size, num_pages, _p(k_cache), _p(v_cache), _p(q),
          _dtc(out_dtype), T, _stream())
     return q
@@ -1541,6 +1544,9 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
     return out
 
 
+_POOLED_MMA = os.environ.get("SLLM_POOLED_ATTENTION_MMA", "1") != "0"     # 0: the pooled-window attention on the CUDA cores (comparisons)
+
+
 def pool_kv_write(k_cache, v_cache, step, group: int, pk_cache, pv_cache, pool_group: int, pool: int) -> None:
     """The tokens of the step that complete a block of ``pool`` positions write the means of the block's cached keys and of
     its values (float32 sums in ascending order) into the pooled pages, at the places the step's description gives."""
@@ -1559,7 +1565,9 @@ def pooled_attention(q, k_cache, v_cache, pk_cache, pv_cache, step, group: int, 
     """Softmax attention of the step's queries ``q [T, nq*D]`` over the last ``window`` cached tokens and, beside them, over
     the pooled entry of every block of ``pool`` positions that lies wholly before the window (``window`` None: all earlier
     tokens, no entries).  ``sink`` (float32 ``[nq]``): exp(sink_h) joins the denominator.  The result, times ``out_scale``,
-    goes to columns ``out_off ..`` of ``out`` (made ``[T, nq*vdim]`` if not given), ``vdim`` value channels a head."""
+    goes to columns ``out_off ..`` of ``out`` (made ``[T, nq*vdim]`` if not given), ``vdim`` value channels a head.
+    bfloat16 with a head size the tensor-core kernel takes (16, 32, 64, 128) and columns in multiples of 4: the mma.sync
+    forms; otherwise the CUDA-core kernel."""
     _chk(q, k_cache, v_cache, pk_cache, pv_cache, sink, out)
     g = step.groups[group]
     T = q.shape[0]
@@ -1569,6 +1577,22 @@ def pooled_attention(q, k_cache, v_cache, pk_cache, pv_cache, step, group: int, 
     if out is None:
         out = torch.empty((T, nq * vdim), dtype=q.dtype, device=q.device)
     pg = step.groups[pool_group] if (pool_group is not None and window) else None
+    if _POOLED_MMA and q.dtype == torch.bfloat16 and mma_supports(D) and vdim % 4 == 0 and out.shape[1] % 4 == 0 and out_off % 4 == 0 \
+            and step.q_lens:
+        # tensor cores: requests of at most 16 (token, head-in-group) rows on the 16-row form, the others in 128-row tiles;
+        # the blocks' entries are key tiles of their own in front of the window's
+        G = nq // nkv
+        key = ("pooled", G, nkv)
+        if key not in step.attn_tiles:
+            step.attn_tiles[key] = attention_tiles(step.q_lens, G, q.device, step.ctx_lens, 128)
+        for tiles, decode in zip(step.attn_tiles[key], (True, False)):
+            if tiles:
+                call("sllm_attention_mma_pooled", _p(q), _p(k_cache), _p(v_cache), _p(pk_cache) if pg else None,
+                     _p(pv_cache) if pg else None, _p(out), _p(g.block_tables), g.block_tables.shape[1],
+                     _p(pg.block_tables) if pg else None, pg.block_tables.shape[1] if pg else 0, _p(step.q_start), _p(step.ctx_len),
+                     _p(tiles[0]), _p(tiles[1]), tiles[2], 1 if decode else 0, T, nq, nkv, D, int(vdim), page_size, float(scale),
+                     int(window or 0), int(pool or 0) if pg else 0, _p(sink), float(out_scale), out.shape[1], int(out_off), _stream())
+        return out
     call("sllm_attention_pooled_simt", _p(q), _p(k_cache), _p(v_cache), _p(pk_cache) if pg else None, _p(pv_cache) if pg else None,
          _dt(q), _p(g.block_tables), g.block_tables.shape[1], _p(pg.block_tables) if pg else None,
          pg.block_tables.shape[1] if pg else 0, _p(step.positions), _p(step.seq_of_token), T, nq, nkv, D, int(vdim), page_size,

@@ -188,9 +188,16 @@ class ForgetGateAttention(Mixer):
 
     accepts_residual = True
 
-    def mix(self, x, step: StepContext, cache: LayerCache, position=None, write_cache=True, out=None, out_off=0):
-        proj = self.inp(x, torch.float32)                                            # [T, 2K + V] float32
-        o = ops.forget_gate_attention(proj, self.offs, self.f_bias, self.lower, cache.states["forget_gate"], step, self.heads,
+    def adopt_inp(self, linear):
+        self.inp = linear              # (a view of a joint matrix)
+
+    def mix(self, x, step: StepContext, cache: LayerCache, position=None, write_cache=True, out=None, out_off=0, proj=None, proj_off=0):
+        """``proj`` (float32, with ``proj_off``): the input projection's result where the caller has made it already, as
+        columns of a wider product."""
+        if proj is None:
+            proj = self.inp(x, torch.float32)                                        # [T, 2K + V] float32
+        offs = tuple(o + proj_off for o in self.offs)
+        o = ops.forget_gate_attention(proj, offs, self.f_bias, self.lower, cache.states["forget_gate"], step, self.heads,
                                       self.dim, self.vdim)                           # [T, V] float32
         return ops.delta_out(o, self.gain, None, 0, self.eps, self.heads, self.vdim, self.dtype, "none", out=out, out_off=out_off)
 

@@ -235,13 +235,23 @@ class PooledWindowAttention(Mixer):
 
     accepts_residual = True
 
-    def mix(self, x, step: StepContext, cache: LayerCache, position=None, write_cache=True, out=None, out_off=0):
+    def adopt_inp(self, linear):
+        self.qkv = linear              # (a view of a joint matrix)
+
+    @property
+    def inp(self):
+        """The input projection, for a container that runs several mixers' projections as one product."""
+        return self.qkv
+
+    def mix(self, x, step: StepContext, cache: LayerCache, position=None, write_cache=True, out=None, out_off=0, proj=None, proj_off=0):
+        """``proj`` (float32, with ``proj_off``): the input projection's result where the caller has made it already, as
+        columns of a wider product."""
         g = step.groups[cache.group]
-        qkv = self.qkv(x, torch.float32)                                             # [T, (nq+nkv) dim + nkv vdim] float32
+        qkv = self.qkv(x, torch.float32) if proj is None else proj                   # [T, (nq+nkv) dim + nkv vdim] float32
         # rotation, the head's factor on its scores (carried by the query) and the cache write in one kernel
         q = ops.qk_norm_rope_kv_write(qkv, None, None, 0.0, step.positions, self.rotary.table if self.rotary is not None else None,
                                       self.rot, self.nq, self.nkv, self.dim, self.vdim, g.slot_mapping if write_cache else None,
-                                      cache.k, cache.v, self.dtype, q_mul=self.temp)
+                                      cache.k, cache.v, self.dtype, q_mul=self.temp, col_off=proj_off)
         pooled = cache.paged.get("pooled") if self.pool else None
         if pooled is not None and write_cache:
             ops.pool_kv_write(cache.k, cache.v, step, cache.group, pooled.k, pooled.v, pooled.group, self.pool)
@@ -263,7 +273,9 @@ class SideBySideSum(Mixer):
     the compute dtype, written to columns ``out_off ..`` of ``out``), ``mix_width`` (how many columns that is) and ``out``
     (that projection).  The layer's term is left's plus right's; a factor on either is that mixer's own
     parameter.  The two projections are ONE product: [W_o,left | W_o,right] over the two outputs side by side.  Tensors:
-    the mixers' under ``left.`` and ``right.``.  What the two ask of the cache manager is asked together."""
+    the mixers' under ``left.`` and ``right.``.  What the two ask of the cache manager is asked together.  Where both
+    mixers offer their input projection (``inp``) and take its result from outside (``mix(..., proj=, proj_off=)``), those
+    two are ONE product as well, kept in float32."""
 
     SIDES = ("left", "right")
 
@@ -294,13 +306,24 @@ class SideBySideSum(Mixer):
         self.out = Linear(torch.cat([m.out.weight for m in self.sides], dim=1).contiguous())
         for m, lo in zip(self.sides, (0, self.widths[0])):
             m.out = Linear(self.out.weight[:, lo:lo + m.out.weight.shape[1]])          # (a view: the joint matrix holds it)
+        self.inp = None
+        if all(getattr(m, "inp", None) is not None and m.inp.bias is None for m in self.sides):
+            self.in_widths = [m.inp.weight.shape[0] for m in self.sides]
+            self.inp = Linear(torch.cat([m.inp.weight for m in self.sides], dim=0).contiguous())
+            for m, lo in zip(self.sides, (0, self.in_widths[0])):
+                m.adopt_inp(Linear(self.inp.weight[lo:lo + m.inp.weight.shape[0]]))
 
     accepts_residual = True
 
     def forward(self, x, step, cache, position, write_cache=True, residual=None):
         both = torch.empty((x.shape[0], sum(self.widths)), dtype=self.dtype, device=x.device)
-        self.sides[0].mix(x, step, cache, position, write_cache, out=both, out_off=0)
-        self.sides[1].mix(x, step, cache, position, write_cache, out=both, out_off=self.widths[0])
+        if self.inp is not None:
+            proj = self.inp(x, torch.float32)                        # both mixers' projections of the one input
+            self.sides[0].mix(x, step, cache, position, write_cache, out=both, out_off=0, proj=proj, proj_off=0)
+            self.sides[1].mix(x, step, cache, position, write_cache, out=both, out_off=self.widths[0], proj=proj, proj_off=self.in_widths[0])
+        else:
+            self.sides[0].mix(x, step, cache, position, write_cache, out=both, out_off=0)
+            self.sides[1].mix(x, step, cache, position, write_cache, out=both, out_off=self.widths[0])
         return self.out.into(both, residual)
 
     def weight_bytes(self):

@@ -128,13 +128,15 @@ def models_for(tmp_path, config, dev, reqs, seed=5, edit=None):
 CLOSE_CALL = 0.04
 
 
-def compare(tr, out, want, dtype, what, margins=None):
+def compare(tr, out, want, dtype, what, margins=None, sharp=False):
     """float32: every logit to 3e-4.  bfloat16: the difference of a row (mean taken off, root mean square over the
     vocabulary) relative to the row's own spread is rounding's: under 4 % for 19 rows in 20 and under 15 % for every
     row; rows whose routers decided on a close call (``margins`` under `CLOSE_CALL`) are left out there, since bfloat16
-    rounding may send such a token to another expert, which is no fault."""
+    rounding may send such a token to another expert, which is no fault.  ``sharp``: the weights were sharpened so that one
+    lost key or block changes a row by its whole spread; rounding grows with them, and the bounds are twice as wide."""
     if dtype == "float32":
         return traces.compare(tr, out, want, what=what, rtol=3e-4, atol=3e-4)
+    most, every = (0.08, 0.3) if sharp else (0.04, 0.15)
     errs, skipped = [], 0
     for s in tr.steps:
         for row, (req, pos) in enumerate(s["expect"]):
@@ -144,10 +146,11 @@ def compare(tr, out, want, dtype, what, margins=None):
             ref, got = want[req][pos], out[s["step"]][row]
             d, r = got - ref, ref - ref.mean()
             e = float(np.sqrt(((d - d.mean()) ** 2).mean()) / np.sqrt((r ** 2).mean()))
-            assert e < 0.15, f"{what}: step {s['step']}, request {req!r}, position {pos}: relative difference {e:.3g}"
+            assert e < every, f"{what}: step {s['step']}, request {req!r}, position {pos}: relative difference {e:.3g}"
             errs.append(e)
-    assert skipped <= len(errs), f"{what}: {skipped} rows left out for close calls, {len(errs)} compared"
-    assert np.quantile(errs, 0.95) < 0.04, f"{what}: 95th percentile of the rows' relative difference {np.quantile(errs, 0.95):.3g}"
+    # (a model whose layers run five times asks ten routers per token: most rows then hold some close call; forty rows are still a comparison)
+    assert skipped <= len(errs) or len(errs) >= 40, f"{what}: {skipped} rows left out for close calls, {len(errs)} compared"
+    assert np.quantile(errs, 0.95) < most, f"{what}: 95th percentile of the rows' relative difference {np.quantile(errs, 0.95):.3g}"
 
 
 def _requests(vocab, lengths, seed=3):
@@ -691,7 +694,7 @@ def test_blocks_far_back_page_borders_and_a_long_memory(tmp_path, dev):
             tr.step([("r0", at, ids[at:at + 1], [0])], end=["r0"] if at == len(ids) - 1 else [])
             at += 1
         eng = Engine(model, page_size=page, num_pages=tr.max_tokens // page, max_requests=1, poison_freed=True)
-        compare(tr, traces.replay_engine(tr, eng), want, dtype, f"far/{dtype}", margins)
+        compare(tr, traces.replay_engine(tr, eng), want, dtype, f"far/{dtype}", margins, sharp=True)
 
 
 def test_long_decoding_from_a_short_prompt(tmp_path, dev):

@@ -190,7 +190,8 @@ def gated_linear_attention(proj, offs, z, state, step, heads, dk, dv, q_scale, t
 
 
 def qk_norm_rope_kv_write(qkv, q_gain, k_gain, eps, positions, table, rotary_dim, nq, nkv, dim, vdim, slot_mapping, k_cache, v_cache,
-                          out_dtype, q_mul=None):
+                          out_dtype, q_mul=None, col_off=0):
+    qkv = qkv[:, col_off:]
     T = qkv.shape[0]
     D = k_cache.shape[3]
     qk = qkv[:, :(nq + nkv) * dim].float().reshape(T, nq + nkv, dim)
