@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
   int key_lo = 0;
   if (p.window > 0) key_lo = max(0, pos0 + row0 / G - p.window + 1);
   if (p.block > 0) key_lo = max(key_lo, (pos0 + row0 / G) / p.block * p.block);
-  if (p.num_splits > 1) {
+  if (p.num_splits > 1 && p.out_ld == 0) {
     const int chunk = ((ctx + p.num_splits - 1) / p.num_splits + ATT_BN - 1) / ATT_BN * ATT_BN;
     key_lo = max(key_lo, split * chunk);
     key_hi = min(key_hi, (split + 1) * chunk);
@@ -115,8 +115,16 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
     nb_max = lo_last > 0 ? lo_last / p.pool : 0;
   }
   const int n_ptiles = (nb_max + ATT_BN - 1) / ATT_BN;
-  const int n_tiles = n_ptiles + n_tok_tiles;
+  const int n_all = n_ptiles + n_tok_tiles;
   const int* pt = p.pool > 0 ? p.pool_tables + (size_t)seq * p.pool_max_pages : nullptr;
+  // this CTA's share of the tiles: all of them, or (out_ld > 0: the form with its own output layout) one of num_splits
+  // runs of consecutive tiles, pooled and token tiles alike
+  int t_begin = 0, n_tiles = n_all;
+  if (p.out_ld > 0 && p.num_splits > 1) {
+    const int per = (n_all + p.num_splits - 1) / p.num_splits;
+    t_begin = min(split * per, n_all);
+    n_tiles = min(per, n_all - t_begin);
+  }
 
   // the pages of this CTA's key range, fetched once: a tile's loads then depend on shared
   // memory only, not on a global load of the table
@@ -148,6 +156,7 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
   const size_t head_off = (size_t)kvh * ps * HD + ch8;
   const size_t page_stride = (size_t)p.nkv * ps * HD;
   auto load_kv = [&](int tile, int buf) {
+    tile += t_begin;
     if (tile < n_ptiles) {                        // a tile of pooled entries
 #pragma unroll
       for (int r = r_first; r < ATT_BN; r += R_STEP) {
@@ -252,8 +261,9 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
       }
     }
     // mask, scale (into the log2 domain), row maxima
-    const bool pooled_tile = tile < n_ptiles;
-    const int kbase = (pooled_tile ? tile * ATT_BN : tile0 + (tile - n_ptiles) * ATT_BN) + koff;
+    const int vtile = t_begin + tile;
+    const bool pooled_tile = vtile < n_ptiles;
+    const int kbase = (pooled_tile ? vtile * ATT_BN : tile0 + (vtile - n_ptiles) * ATT_BN) + koff;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int n = 0; n < NT; ++n)
@@ -323,8 +333,8 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
       if (row >= rows_total) continue;
       const size_t orow = (size_t)(q0 + row / G) * p.nq + kvh * G + row % G;
       if (p.sink != nullptr && p.num_splits == 1) l_r[i] += exp2f(p.sink[kvh * G + row % G] * 1.4426950408889634f - m_r[i]);
-      const float inv = l_r[i] > 0.f ? p.out_scale / l_r[i] : 0.f;
-      if (p.out_ld > 0) {
+      const float inv = l_r[i] > 0.f ? (p.num_splits > 1 ? 1.f : p.out_scale) / l_r[i] : 0.f;
+      if (p.out_ld > 0 && p.num_splits == 1) {
         __nv_bfloat16* po = p.out + (size_t)(q0 + row / G) * p.out_ld + p.out_off + (size_t)(kvh * G + row % G) * p.vdim;
 #pragma unroll
         for (int d = 0; d < DT; ++d)
@@ -382,9 +392,9 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
         acc.x += v.x * f[w]; acc.y += v.y * f[w]; acc.z += v.z * f[w]; acc.w += v.w * f[w];
       }
       if (p.sink != nullptr && p.num_splits == 1) lt += exp2f(p.sink[kvh * G + row % G] * 1.4426950408889634f - mt);
-      const float inv = lt > 0.f ? p.out_scale / lt : 0.f;
+      const float inv = lt > 0.f ? (p.num_splits > 1 ? 1.f : p.out_scale) / lt : 0.f;
       const size_t orow = (size_t)(q0 + row / G) * p.nq + kvh * G + row % G;
-      if (p.out_ld > 0) {
+      if (p.out_ld > 0 && p.num_splits == 1) {
         if (d4 < p.vdim) {
           __nv_bfloat16* po = p.out + (size_t)(q0 + row / G) * p.out_ld + p.out_off + (size_t)(kvh * G + row % G) * p.vdim + d4;
           *reinterpret_cast<uint2*>(po) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
@@ -406,7 +416,7 @@ template <int HD>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                              __nv_bfloat16* __restrict__ out, int rows, int num_splits,
                                              const int* __restrict__ tile_seq, const int* __restrict__ q_start, int nq,
-                                             const float* __restrict__ sink) {
+                                             const float* __restrict__ sink, int out_ld, int out_off, int vdim, float out_scale) {
   // One CTA per (tile, query head, token of the tile's request): the rows the decode form wrote and no others, so
   // that a step's other rows (a prompt portion's, the prefill form's) are neither read nor touched.  The step's
   // description is read before the wait for the kernel before.
@@ -424,14 +434,17 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
     tot += l == -INFINITY ? 0.f : exp2f(l - mt);
   }
   if (sink != nullptr) tot += exp2f(sink[blockIdx.y] * 1.4426950408889634f - mt);
-  const float inv = tot > 0.f ? 1.f / tot : 0.f;
-  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+  const float inv = tot > 0.f ? out_scale / tot : 0.f;
+  // (out_ld > 0: the row of token t and head h lies at out + t * out_ld + out_off + h * vdim and holds vdim channels)
+  __nv_bfloat16* po = out_ld > 0 ? out + (size_t)(q0 + (int)blockIdx.z) * out_ld + out_off + (size_t)blockIdx.y * vdim : out + (size_t)row * HD;
+  const int lim = out_ld > 0 ? vdim : HD;
+  for (int d = threadIdx.x; d < lim; d += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < num_splits; ++s) {
       const float l = part_lse[(size_t)s * rows + row];
       if (l != -INFINITY) acc += part_o[((size_t)s * rows + row) * HD + d] * exp2f(l - mt);
     }
-    out[(size_t)row * HD + d] = __float2bfloat16_rn(acc * inv);
+    po[d] = __float2bfloat16_rn(acc * inv);
   }
 }
 
@@ -457,7 +470,7 @@ static int launch_attention(const AttnParams& p, int tiles, cudaStream_t stream)
     const int G = p.nq / p.nkv;
     launch_kernel(attention_combine_kernel<HD>, dim3((unsigned)tiles, (unsigned)p.nq, (unsigned)(16 / G > 0 ? 16 / G : 1)), HD >= 128 ? 128 : 64, 0, stream,
                   (const float*)p.part_o, (const float*)p.part_lse, p.out, p.total_tokens * p.nq, p.num_splits, p.tile_seq,
-                  p.q_start, p.nq, p.sink);
+                  p.q_start, p.nq, p.sink, p.out_ld, p.out_off, p.vdim, p.out_scale);
     rc = launch_status("attention_combine");
   }
   return rc;
@@ -504,14 +517,18 @@ SLLM_EXPORT int sllm_attention_mma(const void* q, const void* k_cache, const voi
   return SLLM_ERR_UNSUPPORTED;
 }
 
-// The same kernels over a window of tokens plus pooled blocks (see `AttnParams`): no split of the context; the result,
-// times `out_scale`, goes to columns out_off + h * vdim of rows of `out_ld` elements.
+// The same kernels over a window of tokens plus pooled blocks (see `AttnParams`); the result, times `out_scale`, goes to
+// columns out_off + h * vdim of rows of `out_ld` elements.  The 16-row form may cut its tiles (pooled and token tiles
+// alike) into `num_splits` runs that CTAs of their own walk; the merge kernel then writes the rows.
 SLLM_EXPORT int sllm_attention_mma_pooled(const void* q, const void* k_cache, const void* v_cache, const void* pk_cache,
                                           const void* pv_cache, void* out, const int* block_tables, int max_pages,
                                           const int* pool_tables, int pool_max_pages, const int* q_start, const int* ctx_len,
-                                          const int* tile_seq, const int* tile_row0, int tiles, int decode, int total_tokens,
+                                          const int* tile_seq, const int* tile_row0, int tiles, int decode, int num_splits,
+                                          float* part_o, float* part_lse, int total_tokens,
                                           int nq, int nkv, int hd, int vdim, int page_size, float scale, int window, int pool,
                                           const float* sink, float out_scale, int out_ld, int out_off, cudaStream_t stream) {
+  SLLM_REQUIRE(num_splits >= 1 && num_splits <= 65535 && (num_splits == 1 || (decode && part_o && part_lse)),
+               "attention_mma_pooled: %d runs of tiles need the 16-row form and scratch", num_splits);
   SLLM_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_mma_pooled: bad head counts nq=%d nkv=%d", nq, nkv);
   SLLM_REQUIRE(sllm_attention_mma_supports(hd), "attention_mma_pooled: head_dim=%d is not one of 16, 32, 64, 128", hd);
   SLLM_REQUIRE(page_size > 0 && max_pages > 0 && tiles >= 0 && total_tokens >= 0 && nkv <= 65535, "attention_mma_pooled: bad sizes");
@@ -524,10 +541,10 @@ SLLM_EXPORT int sllm_attention_mma_pooled(const void* q, const void* k_cache, co
   if (tiles == 0) return SLLM_OK;
   AttnParams p;
   p.q = (const __nv_bfloat16*)q; p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
-  p.out = (__nv_bfloat16*)out; p.part_o = nullptr; p.part_lse = nullptr; p.block_tables = block_tables;
+  p.out = (__nv_bfloat16*)out; p.part_o = part_o; p.part_lse = part_lse; p.block_tables = block_tables;
   p.q_start = q_start; p.ctx_len = ctx_len; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
   p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.window = window; p.block = 0;
-  p.num_splits = 1; p.total_tokens = total_tokens;
+  p.num_splits = num_splits; p.total_tokens = total_tokens;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.sink = sink;
   p.pk_cache = (const __nv_bfloat16*)pk_cache; p.pv_cache = (const __nv_bfloat16*)pv_cache; p.pool_tables = pool_tables;

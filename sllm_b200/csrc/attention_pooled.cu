@@ -11,8 +11,8 @@
 //                            pages, adds them in ascending order in float32 and writes their means.
 //   attention_pooled_simt    CUDA cores, float32 arithmetic, one CTA per (token, query head): any head size up to 256,
 //                            float32 or bfloat16 caches.  Prompt portions and single decoded tokens are the same work.
-//   attention_pooled_mma     bfloat16 tensor cores (mma.sync m16n8k16): a CTA per (16-row tile of a request's portion,
-//                            kv head) with the group's query heads stacked along the rows' dimension of the grid.
+//   (bfloat16 heads of 16, 32, 64 or 128 channels run on the tensor cores instead: the mma.sync forms of
+//   attention_mma.cu walk tiles of the blocks' entries in front of the window's token tiles.)
 //
 // Each warp of the CUDA-core form takes the row's keys w, w+W, w+2W, ... (pooled entries first, then tokens) in ascending
 // order with an online softmax; the warps' partial results are merged in warp order.  The order depends on the position
@@ -40,14 +40,31 @@ pool_kv_write_kernel(const TC* __restrict__ k_cache, const TC* __restrict__ v_ca
   const int pos = positions[t];
   const int* bt = block_tables + (size_t)seq_of_token[t] * max_pages;
   const size_t dst = (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * D;
+  // eight tokens' loads are in flight together; the sums still run in ascending order of the tokens
+  constexpr int U = 8;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float sk = 0.f, sv = 0.f;
-    for (int j = pos - pool + 1; j <= pos; ++j) {
-      const int page = j >= 0 ? bt[j / page_size] : -1;
-      if (page < 0) continue;
-      const size_t row = (((size_t)page * nkv + kvh) * page_size + (j % page_size)) * D + d;
-      sk += to_f32(k_cache[row]);
-      sv += to_f32(v_cache[row]);
+    for (int j0 = pos - pool + 1; j0 <= pos; j0 += U) {
+      size_t row[U];
+      bool ok[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int j = j0 + u;
+        const int page = (j >= 0 && j <= pos) ? bt[j / page_size] : -1;
+        ok[u] = page >= 0;
+        row[u] = ok[u] ? (((size_t)page * nkv + kvh) * page_size + (j % page_size)) * D + d : 0;
+      }
+      float kk[U], vv[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        kk[u] = ok[u] ? to_f32(k_cache[row[u]]) : 0.f;
+        vv[u] = ok[u] ? to_f32(v_cache[row[u]]) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        sk += kk[u];
+        sv += vv[u];
+      }
     }
     pk_cache[dst + d] = from_f32<TC>(sk / (float)pool);
     pv_cache[dst + d] = from_f32<TC>(sv / (float)pool);

@@ -1547,6 +1547,16 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
 _POOLED_MMA = os.environ.get("SLLM_POOLED_ATTENTION_MMA", "1") != "0"     # 0: the pooled-window attention on the CUDA cores (comparisons)
 
 
+@functools.lru_cache(maxsize=4096)
+def pooled_splits(num_small: int, nkv: int, max_ctx: int, window: int, pool: int) -> int:
+    """Into how many runs of 64-key tiles the 16-row form of the pooled-window attention cuts a request's keys (the blocks'
+    entries and the window's tokens): enough CTAs for two an SM, at least two tiles a run, at most 16 runs."""
+    keys = min(window, max_ctx) if window else max_ctx
+    tiles = -(-keys // 64) + 1 + (-(-(max_ctx // pool) // 64) if pool else 0)
+    want = (2 * num_sms()) // max(1, num_small * nkv)
+    return max(1, min(want, tiles // 2, 16))
+
+
 def pool_kv_write(k_cache, v_cache, step, group: int, pk_cache, pv_cache, pool_group: int, pool: int) -> None:
     """The tokens of the step that complete a block of ``pool`` positions write the means of the block's cached keys and of
     its values (float32 sums in ascending order) into the pooled pages, at the places the step's description gives."""
@@ -1587,10 +1597,18 @@ def pooled_attention(q, k_cache, v_cache, pk_cache, pv_cache, step, group: int, 
             step.attn_tiles[key] = attention_tiles(step.q_lens, G, q.device, step.ctx_lens, 128)
         for tiles, decode in zip(step.attn_tiles[key], (True, False)):
             if tiles:
+                splits, part_o, part_lse = 1, None, None
+                if decode:
+                    splits = pooled_splits(tiles[2], nkv, step.max_ctx_len, int(window or 0), int(pool or 0) if pg else 0)
+                if splits > 1:
+                    part_o = torch.empty((splits, T, nq, D), dtype=torch.float32, device=q.device)
+                    part_lse = torch.empty((splits, T, nq), dtype=torch.float32, device=q.device)
+                    launches["own"] += 1          # the merge kernel
                 call("sllm_attention_mma_pooled", _p(q), _p(k_cache), _p(v_cache), _p(pk_cache) if pg else None,
                      _p(pv_cache) if pg else None, _p(out), _p(g.block_tables), g.block_tables.shape[1],
                      _p(pg.block_tables) if pg else None, pg.block_tables.shape[1] if pg else 0, _p(step.q_start), _p(step.ctx_len),
-                     _p(tiles[0]), _p(tiles[1]), tiles[2], 1 if decode else 0, T, nq, nkv, D, int(vdim), page_size, float(scale),
+                     _p(tiles[0]), _p(tiles[1]), tiles[2], 1 if decode else 0, splits, _p(part_o), _p(part_lse), T, nq, nkv, D,
+                     int(vdim), page_size, float(scale),
                      int(window or 0), int(pool or 0) if pg else 0, _p(sink), float(out_scale), out.shape[1], int(out_off), _stream())
         return out
     call("sllm_attention_pooled_simt", _p(q), _p(k_cache), _p(v_cache), _p(pk_cache) if pg else None, _p(pv_cache) if pg else None,

@@ -120,7 +120,8 @@ def _declare(L):
                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
         "sllm_attention_mma_pooled": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                                      c_int, c_int, c_int,
                                       c_int, c_float, c_int, c_int, c_void_p, c_float, c_int, c_int, c_void_p],
         "sllm_post_add_norm": [c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_float, c_void_p, c_float, c_void_p, c_int, c_int,
                                c_int, c_void_p],
