@@ -8,7 +8,8 @@
 //
 //   pool_kv_write            the token that completes a block (its place in the pooled pages comes with the step's
 //                            description, -1 for every other token) reads the block's keys and values from the token
-//                            pages, adds them in ascending order in float32 and writes their means.
+//                            pages, adds them in float32 (in an order that depends on the block's length alone) and
+//                            writes their means.
 //   attention_pooled_simt    CUDA cores, float32 arithmetic, one CTA per (token, query head): any head size up to 256,
 //                            float32 or bfloat16 caches.  Prompt portions and single decoded tokens are the same work.
 //   (bfloat16 heads of 16, 32, 64 or 128 channels run on the tensor cores instead: the mma.sync forms of
@@ -26,12 +27,18 @@ namespace sllm {
 constexpr int AP_WARPS = 4;
 constexpr int AP_MAX_D = 256;
 
+constexpr int PW_WARPS = 8;
+
+// grid (T, nkv), 8 warps: warp w adds the block's tokens w, w+8, w+16, ... in ascending order (a lane holds every 32nd
+// channel; the loads of up to eight tokens are in flight together), then the warps' sums are added in warp order.  The
+// order depends on the block's length alone.
 template <typename TC>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(PW_WARPS * 32)
 pool_kv_write_kernel(const TC* __restrict__ k_cache, const TC* __restrict__ v_cache, const int* __restrict__ block_tables,
                      int max_pages, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                      const int* __restrict__ pool_slots, TC* __restrict__ pk_cache, TC* __restrict__ pv_cache, int pool_pages,
                      int nkv, int D, int page_size, int pool) {
+  extern __shared__ float pw_sm[];               // [2][PW_WARPS][D]
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, kvh = blockIdx.y;
@@ -39,32 +46,42 @@ pool_kv_write_kernel(const TC* __restrict__ k_cache, const TC* __restrict__ v_ca
   if (slot < 0 || slot / page_size >= pool_pages) return;
   const int pos = positions[t];
   const int* bt = block_tables + (size_t)seq_of_token[t] * max_pages;
-  const size_t dst = (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * D;
-  // eight tokens' loads are in flight together; the sums still run in ascending order of the tokens
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int first = pos - pool + 1;
   constexpr int U = 8;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+  for (int d0 = 0; d0 < D; d0 += 32) {
+    const int d = d0 + lane;
     float sk = 0.f, sv = 0.f;
-    for (int j0 = pos - pool + 1; j0 <= pos; j0 += U) {
-      size_t row[U];
-      bool ok[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int j = j0 + u;
-        const int page = (j >= 0 && j <= pos) ? bt[j / page_size] : -1;
-        ok[u] = page >= 0;
-        row[u] = ok[u] ? (((size_t)page * nkv + kvh) * page_size + (j % page_size)) * D + d : 0;
-      }
+    for (int i0 = warp; i0 < pool; i0 += PW_WARPS * U) {
       float kk[U], vv[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        kk[u] = ok[u] ? to_f32(k_cache[row[u]]) : 0.f;
-        vv[u] = ok[u] ? to_f32(v_cache[row[u]]) : 0.f;
+        const int i = i0 + u * PW_WARPS, j = first + i;
+        const int page = (i < pool && j >= 0) ? bt[j / page_size] : -1;
+        const bool ok = page >= 0 && d < D;
+        const size_t row = ok ? (((size_t)page * nkv + kvh) * page_size + (j % page_size)) * D + d : 0;
+        kk[u] = ok ? to_f32(k_cache[row]) : 0.f;
+        vv[u] = ok ? to_f32(v_cache[row]) : 0.f;
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         sk += kk[u];
         sv += vv[u];
       }
+    }
+    if (d < D) {
+      pw_sm[warp * D + d] = sk;
+      pw_sm[(PW_WARPS + warp) * D + d] = sv;
+    }
+  }
+  __syncthreads();
+  const size_t dst = (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float sk = 0.f, sv = 0.f;
+#pragma unroll
+    for (int w = 0; w < PW_WARPS; ++w) {
+      sk += pw_sm[w * D + d];
+      sv += pw_sm[(PW_WARPS + w) * D + d];
     }
     pk_cache[dst + d] = from_f32<TC>(sk / (float)pool);
     pv_cache[dst + d] = from_f32<TC>(sv / (float)pool);
@@ -175,11 +192,13 @@ SLLM_EXPORT int sllm_pool_kv_write(const void* k_cache, const void* v_cache, int
   SLLM_REQUIRE(nkv <= 65535, "pool_kv_write: %d kv heads exceed one launch", nkv);
   if (T == 0 || pool_pages == 0) return SLLM_OK;
   const dim3 grid(T, nkv);
+  const size_t smem = 2 * (size_t)PW_WARPS * D * sizeof(float);
+  SLLM_REQUIRE(smem <= 48 * 1024, "pool_kv_write: a head of %d channels is more than the kernel keeps in shared memory", D);
   if (dtype == SLLM_F32)
-    launch_kernel(pool_kv_write_kernel<float>, grid, 128, 0, stream, (const float*)k_cache, (const float*)v_cache, block_tables,
+    launch_kernel(pool_kv_write_kernel<float>, grid, PW_WARPS * 32, smem, stream, (const float*)k_cache, (const float*)v_cache, block_tables,
                   max_pages, positions, seq_of_token, pool_slots, (float*)pk_cache, (float*)pv_cache, pool_pages, nkv, D, page_size, pool);
   else if (dtype == SLLM_BF16)
-    launch_kernel(pool_kv_write_kernel<__nv_bfloat16>, grid, 128, 0, stream, (const __nv_bfloat16*)k_cache,
+    launch_kernel(pool_kv_write_kernel<__nv_bfloat16>, grid, PW_WARPS * 32, smem, stream, (const __nv_bfloat16*)k_cache,
                   (const __nv_bfloat16*)v_cache, block_tables, max_pages, positions, seq_of_token, pool_slots,
                   (__nv_bfloat16*)pk_cache, (__nv_bfloat16*)pv_cache, pool_pages, nkv, D, page_size, pool);
   else

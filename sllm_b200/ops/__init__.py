@@ -1559,7 +1559,7 @@ def pooled_splits(num_small: int, nkv: int, max_ctx: int, window: int, pool: int
 
 def pool_kv_write(k_cache, v_cache, step, group: int, pk_cache, pv_cache, pool_group: int, pool: int) -> None:
     """The tokens of the step that complete a block of ``pool`` positions write the means of the block's cached keys and of
-    its values (float32 sums in ascending order) into the pooled pages, at the places the step's description gives."""
+    its values (float32 sums in an order that depends on the block's length alone) into the pooled pages, at the places the step's description gives."""
     _chk(k_cache, v_cache, pk_cache, pv_cache)
     g, pg = step.groups[group], step.groups[pool_group]
     num_pages, nkv, page_size, D = k_cache.shape
