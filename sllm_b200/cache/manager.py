@@ -44,8 +44,9 @@ class CacheManager:
     def __init__(self, needs, *, page_size: int, num_pages, max_requests: int, poison_freed: bool = False):
         """``needs``: per run ``("own", PagedKV|SlotState|None)``, or a tuple of those (at most one
         of them paged; states with different names), or ``("borrow", run)``, or ``("borrow", run, states)`` for a run that
-        reads another run's pages and keeps `SlotState`s of its own (`CausalLM.cache_needs`).  ``num_pages``: pages per group (an int for all
-        groups, or one per group).  ``poison_freed`` (a debugging aid, off by default): a page
+        reads another run's pages and keeps `SlotState`s of its own (`CausalLM.cache_needs`).  ``num_pages``: pages per group (one number
+        per group, or an int: that many pages for every group of an entry per token, and for a group of one entry per
+        ``stride`` tokens the pages that hold as many tokens' entries, plus one per request).  ``poison_freed`` (a debugging aid, off by default): a page
         that goes back to its pool is filled with NaN in every layer and zeroed again when it is
         handed out, so that a read of a page the reader no longer holds shows in the logits."""
         self.poison_freed = bool(poison_freed)
@@ -90,7 +91,9 @@ class CacheManager:
                 else:
                     raise TypeError(f"run {run}: unknown cache need {need!r}")
         if isinstance(num_pages, int):
-            num_pages = [num_pages] * len(self.groups)
+            # pages for so many tokens' worth of entries: a group of one entry per `stride` tokens needs a `stride`-th of
+            # them, and one page more per request for the page each request has begun
+            num_pages = [num_pages if g.need.stride == 1 else -(-num_pages // g.need.stride) + self.max_requests for g in self.groups]
         if len(num_pages) != len(self.groups):
             raise ValueError(f"num_pages names {len(num_pages)} groups, the model has {len(self.groups)}")
         # ids are best held in runs of a 64-key tile's pages (see pools.py)

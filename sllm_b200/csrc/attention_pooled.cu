@@ -29,16 +29,32 @@ constexpr int AP_MAX_D = 256;
 
 constexpr int PW_WARPS = 8;
 
-// grid (T, nkv), 8 warps: warp w adds the block's tokens w, w+8, w+16, ... in ascending order (a lane holds every 32nd
-// channel; the loads of up to eight tokens are in flight together), then the warps' sums are added in warp order.  The
-// order depends on the block's length alone.
-template <typename TC>
+__device__ __forceinline__ void pw_add(float* acc, const uint4& raw, float) {
+  acc[0] += __uint_as_float(raw.x); acc[1] += __uint_as_float(raw.y); acc[2] += __uint_as_float(raw.z); acc[3] += __uint_as_float(raw.w);
+}
+__device__ __forceinline__ void pw_add(float* acc, const uint4& raw, __nv_bfloat16) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 f = __bfloat1622float2(h[k]);
+    acc[2 * k] += f.x;
+    acc[2 * k + 1] += f.y;
+  }
+}
+
+// grid (T, nkv), 8 warps: warp w adds the block's tokens w, w+8, w+16, ... in ascending order, then the warps' sums are
+// added in warp order: the order depends on the block's length alone.  A lane holds 16 bytes of a row (VEC: rows whose
+// length is a multiple of that; else one channel), so a warp's load instruction fetches a whole row of up to 256 bfloat16
+// channels, and the loads of eight rows are in flight together: a block of 64 tokens is two round trips to memory.
+template <typename TC, bool VEC>
 __global__ void __launch_bounds__(PW_WARPS * 32)
 pool_kv_write_kernel(const TC* __restrict__ k_cache, const TC* __restrict__ v_cache, const int* __restrict__ block_tables,
                      int max_pages, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                      const int* __restrict__ pool_slots, TC* __restrict__ pk_cache, TC* __restrict__ pv_cache, int pool_pages,
                      int nkv, int D, int page_size, int pool) {
   extern __shared__ float pw_sm[];               // [2][PW_WARPS][D]
+  constexpr int E = VEC ? 16 / (int)sizeof(TC) : 1;
+  constexpr int U = 8;
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, kvh = blockIdx.y;
@@ -48,30 +64,53 @@ pool_kv_write_kernel(const TC* __restrict__ k_cache, const TC* __restrict__ v_ca
   const int* bt = block_tables + (size_t)seq_of_token[t] * max_pages;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int first = pos - pool + 1;
-  constexpr int U = 8;
-  for (int d0 = 0; d0 < D; d0 += 32) {
-    const int d = d0 + lane;
-    float sk = 0.f, sv = 0.f;
+  for (int d0 = 0; d0 < D; d0 += 32 * E) {
+    const int d = d0 + lane * E;
+    float sk[E], sv[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) sk[e] = sv[e] = 0.f;
     for (int i0 = warp; i0 < pool; i0 += PW_WARPS * U) {
-      float kk[U], vv[U];
+      size_t row[U];
+      bool ok[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int i = i0 + u * PW_WARPS, j = first + i;
         const int page = (i < pool && j >= 0) ? bt[j / page_size] : -1;
-        const bool ok = page >= 0 && d < D;
-        const size_t row = ok ? (((size_t)page * nkv + kvh) * page_size + (j % page_size)) * D + d : 0;
-        kk[u] = ok ? to_f32(k_cache[row]) : 0.f;
-        vv[u] = ok ? to_f32(v_cache[row]) : 0.f;
+        ok[u] = page >= 0 && d < D;
+        row[u] = ok[u] ? (((size_t)page * nkv + kvh) * page_size + (j % page_size)) * D + d : 0;
       }
+      if constexpr (VEC) {
+        uint4 kk[U], vv[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        sk += kk[u];
-        sv += vv[u];
+        for (int u = 0; u < U; ++u) {
+          kk[u] = ok[u] ? *reinterpret_cast<const uint4*>(k_cache + row[u]) : make_uint4(0u, 0u, 0u, 0u);
+          vv[u] = ok[u] ? *reinterpret_cast<const uint4*>(v_cache + row[u]) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          pw_add(sk, kk[u], TC());
+          pw_add(sv, vv[u], TC());
+        }
+      } else {
+        float kk[U], vv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          kk[u] = ok[u] ? to_f32(k_cache[row[u]]) : 0.f;
+          vv[u] = ok[u] ? to_f32(v_cache[row[u]]) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          sk[0] += kk[u];
+          sv[0] += vv[u];
+        }
       }
     }
     if (d < D) {
-      pw_sm[warp * D + d] = sk;
-      pw_sm[(PW_WARPS + warp) * D + d] = sv;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        pw_sm[warp * D + d + e] = sk[e];
+        pw_sm[(PW_WARPS + warp) * D + d + e] = sv[e];
+      }
     }
   }
   __syncthreads();
@@ -194,15 +233,16 @@ SLLM_EXPORT int sllm_pool_kv_write(const void* k_cache, const void* v_cache, int
   const dim3 grid(T, nkv);
   const size_t smem = 2 * (size_t)PW_WARPS * D * sizeof(float);
   SLLM_REQUIRE(smem <= 48 * 1024, "pool_kv_write: a head of %d channels is more than the kernel keeps in shared memory", D);
-  if (dtype == SLLM_F32)
-    launch_kernel(pool_kv_write_kernel<float>, grid, PW_WARPS * 32, smem, stream, (const float*)k_cache, (const float*)v_cache, block_tables,
-                  max_pages, positions, seq_of_token, pool_slots, (float*)pk_cache, (float*)pv_cache, pool_pages, nkv, D, page_size, pool);
-  else if (dtype == SLLM_BF16)
-    launch_kernel(pool_kv_write_kernel<__nv_bfloat16>, grid, PW_WARPS * 32, smem, stream, (const __nv_bfloat16*)k_cache,
-                  (const __nv_bfloat16*)v_cache, block_tables, max_pages, positions, seq_of_token, pool_slots,
-                  (__nv_bfloat16*)pk_cache, (__nv_bfloat16*)pv_cache, pool_pages, nkv, D, page_size, pool);
-  else
-    SLLM_REQUIRE(false, "pool_kv_write: unknown dtype %d", dtype);
+  auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  const bool vec = aligned(k_cache) && aligned(v_cache) && D % (dtype == SLLM_F32 ? 4 : 8) == 0;
+#define SLLM_PW(TC, VEC_)                                                                                                      \
+  launch_kernel(pool_kv_write_kernel<TC, VEC_>, grid, PW_WARPS * 32, smem, stream, (const TC*)k_cache, (const TC*)v_cache,      \
+                block_tables, max_pages, positions, seq_of_token, pool_slots, (TC*)pk_cache, (TC*)pv_cache, pool_pages, nkv, D, \
+                page_size, pool)
+  if (dtype == SLLM_F32) { if (vec) SLLM_PW(float, true); else SLLM_PW(float, false); }
+  else if (dtype == SLLM_BF16) { if (vec) SLLM_PW(__nv_bfloat16, true); else SLLM_PW(__nv_bfloat16, false); }
+  else SLLM_REQUIRE(false, "pool_kv_write: unknown dtype %d", dtype);
+#undef SLLM_PW
   return launch_status("pool_kv_write");
 }
 
