@@ -464,7 +464,7 @@ def gerupel_config(sz: dict) -> dict:
     W, H, D = sz["width"], sz["heads"], sz["dim"]
     mlp = {"kind": "moe", "expert": {"ff": sz["ff"] // 4 // 64 * 64}, "router": {"experts": 8, "top": 2, "scale": 2.0}}
     left = {"heads": H, "kv_heads": max(1, H // 8), "dim": D, "vdim": D, "mask": {"size": 1024, "pool": 64}, "scale": D ** -0.5,
-            "rot": {"base": 10000.0, "dims": D // 2, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 2048}}}
+            "rot": {"base": 10000.0, "dims": D // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}
     right = {"heads": W // 128, "dim": 128, "vdim": 128}
     layer = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}, "mlp": mlp}
     n = max(sz["layers"] - 2, 2)

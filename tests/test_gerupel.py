@@ -53,8 +53,8 @@ CONFIG_B = {          # heads of 64 on pages of 16 (the tensor-core attention fo
     "architecture": "Gerupel", "vocab": 200, "width": 128, "residual_mult": 0.5, "norm": {"eps": 1e-6},
     "loop": {"start": 0, "stop": 1, "times": 3},
     "layers": [
-        {"type": "parallel", "mixer": _mixer(_left(8, 2, 64, 64, 0.125, 32, 8, rot=32, scaling={"factor": 8.0, "low": 1.0, "high": 4.0, "original": 96}),
-                                             (2, 32, 48), 1.2, 0.5), "mlp": _moe(8, 2, 32, 2.0)},
+        {"type": "parallel", "mixer": _mixer(_left(8, 2, 64, 64, 0.11, 32, 8, rot=16, scaling={"factor": 8.0, "low": 1.0, "high": 6.0, "original": 96}),
+                                             (2, 32, 48), 1.1, 0.7), "mlp": _moe(8, 2, 32, 1.8)},
         {"type": "parallel", "mixer": _mixer(_left(4, 4, 64, 32, 0.11, 24, 16, rot=64), (4, 16, 16), 1.0, 0.8), "mlp": _moe(4, 4, 64, 1.0)},
         {"type": "parallel", "mixer": _mixer(_left(6, 1, 32, 64, 0.18, 48, 12, rot=8, base=100.0), (1, 64, 64), 0.6, 1.4), "mlp": None},
     ],
@@ -279,7 +279,7 @@ def test_pages_of_one_entry_per_block_in_the_cache_manager_and_the_packer():
 
 def test_rotation_frequencies_in_three_regimes():
     from sllm_b200.parts.standard import Rotary
-    for base, dims, sc in ((10000.0, 32, {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 512}), (500.0, 8, SCALING), (100.0, 64, None),
+    for base, dims, sc in ((10000.0, 24, {"factor": 6.0, "low": 1.0, "high": 8.0, "original": 256}), (500.0, 8, SCALING), (100.0, 64, None),
                            (10000.0, 16, {"factor": 2.0, "low": 2.0, "high": 3.0, "original": 40})):
         f, mag = Rotary.frequencies(base, dims, sc)
         want = plain.rotary_frequencies(base, dims, sc)
@@ -407,7 +407,7 @@ ATT_CUTS = [(40, 1, 7), (1, 2, 30), (2, 9, 1), (13, 1, 1), (1, 1, 64), (300, 300
 
 
 @pytest.mark.parametrize("H,G,D,vdim,window,pool,ps", [(4, 2, 16, 16, 12, 5, 8), (3, 3, 24, 10, 6, 9, 4), (8, 1, 64, 64, 32, 8, 16),
-                                                       (2, 1, 40, 40, 1, 1, 16), (6, 2, 128, 96, 40, 16, 16), (2, 2, 200, 7, 16, 16, 32)])
+                                                       (2, 1, 40, 40, 1, 1, 16), (6, 2, 128, 96, 44, 12, 16), (2, 2, 200, 7, 16, 16, 32)])
 def test_window_and_pooled_blocks_in_portions_and_single_tokens(dev, H, G, D, vdim, window, pool, ps):
     """Portions of many sizes beside single tokens, three sequences in shuffled pages (pages nobody wrote hold NaN): every
     query's window edge, every block's first appearance, and the sequence's first tokens are among the rows compared."""
@@ -434,7 +434,7 @@ def test_single_tokens_over_many_tiles_cut_into_runs(D, vdim, window, pool):
         np.testing.assert_allclose(g[-20:], w[-20:], rtol=2e-2, atol=2e-2)
 
 
-@pytest.mark.parametrize("window,pool,ps", [(12, 5, 8), (40, 16, 16), (8, 8, 4), (5, 13, 16)])
+@pytest.mark.parametrize("window,pool,ps", [(12, 5, 8), (36, 12, 16), (8, 8, 4), (5, 13, 16)])
 def test_a_key_that_stands_out_just_inside_and_outside_the_window_and_in_a_block_far_back(dev, window, pool, ps):
     """One key (or one block's keys) lines up with the last query many times more than any other.  Just inside the window
     the output IS that key's value; one token further back the key is gone (its block is not complete before the window);
@@ -671,7 +671,7 @@ LONG_MEMORY = {       # blocks far back matter (sharp attention) and the recurre
     "loop": {"start": 0, "stop": 2, "times": 2},
     "layers": [
         {"type": "parallel", "mixer": _mixer(_left(4, 2, 32, 32, 0.2, 24, 6, rot=16, scaling=SCALING), (2, 32, 32), 1.0, 1.0), "mlp": _moe(4, 2, 32, 1.0)},
-        {"type": "parallel", "mixer": _mixer(_left(2, 1, 64, 48, 0.15, 40, 16, rot=32), (1, 64, 32), 1.0, 1.0), "mlp": None},
+        {"type": "parallel", "mixer": _mixer(_left(2, 1, 64, 48, 0.15, 36, 12, rot=32), (1, 64, 32), 1.0, 1.0), "mlp": None},
     ],
 }
 
